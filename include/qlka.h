@@ -1,0 +1,119 @@
+/* C ABI of the sorted-scan kernel-attention operators for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers (float32, contiguous, all on the current
+ * device), sizes and a CUDA stream, enqueues its kernels on that stream and returns at once
+ * with a status code; nothing throws and no host synchronisation happens. Outputs are
+ * written to caller-allocated buffers. Scratch memory is a caller-allocated workspace whose
+ * size the matching *_workspace_bytes function reports; its contents are meaningless between
+ * calls. Inputs are never modified.
+ *
+ * Shapes (row-major): q (P, D, M) queries, k (P, D, N) keys, v (P, N, C) values,
+ * g_w / g (P, M, C), g_u (P, M), with P = batch * heads.
+ *
+ * Limits shared by all entry points (those of the reference's check_qkv,
+ * Weighted_Abs_Sum/csrc/binding.cpp:69-84 and Weighted_Laplace_Sum/csrc/binding.cpp:66-79):
+ * P, D, N, M > 0, 1 <= C <= 128, N, M <= 131072, P * D * max(N, M) <= INT32_MAX.
+ */
+#ifndef QLKA_H
+#define QLKA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* qlka_stream_t;   /* a cudaStream_t */
+
+enum qlka_status {
+    QLKA_OK = 0,
+    QLKA_ERR_BAD_SHAPE = 1,        /* a size is <= 0 */
+    QLKA_ERR_C_RANGE = 2,          /* C outside [1, 128] */
+    QLKA_ERR_LENGTH = 3,           /* N or M above 131072 */
+    QLKA_ERR_INT32 = 4,            /* P * D * max(N, M) does not fit int32 */
+    QLKA_ERR_PATH = 5,             /* path not in {-1, 0, 1} */
+    QLKA_ERR_FUSED_UNAVAILABLE = 6,/* path == 1 pinned but max(N, M) > 4096 */
+    QLKA_ERR_NULL = 7,             /* a required pointer is NULL */
+    QLKA_ERR_WORKSPACE = 8,        /* workspace too small or misaligned (256 bytes) */
+    QLKA_ERR_CUDA = 9,             /* a CUDA runtime call failed; see qlka_last_cuda_error */
+    QLKA_ERR_UNSUPPORTED = 10      /* a size inside the limits that this build has no kernel for */
+};
+
+/* Human-readable text of a status code (static storage). */
+const char* qlka_status_string(int status);
+/* cudaError_t of the last failing runtime call made by this library on the calling thread. */
+int qlka_last_cuda_error(void);
+
+/* ---- weighted Laplace sum, forward only ------------------------------------------------
+ * out_w[p,m,c] = sum_{d,n} exp(-|k[p,d,n] - q[p,d,m]|) v[p,n,c]     (P, M, C)
+ * out_u[p,m]   = sum_{d,n} exp(-|k[p,d,n] - q[p,d,m]|)              (P, M)
+ * Replaces weighted_laplace_sum_forward, Weighted_Laplace_Sum/csrc/binding.cpp:63-100
+ * (Python: Weighted_Laplace_Sum/weighted_laplace_sum/__init__.py:4-13). */
+int qlka_laplace_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes);
+int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const float* v,
+                                      float* out_w, float* out_u,
+                                      void* workspace, size_t workspace_bytes,
+                                      int P, int D, int N, int M, int C, qlka_stream_t stream);
+
+/* Diagnostic: the same call, but it waits for completion and reports the device time of the
+ * sort/rank kernel and of the walk kernel (CUDA events on `stream`), in milliseconds.
+ * The reference has no counterpart; its benchmark times whole calls
+ * (Experiments/speed_and_memory/bench.py:83-121). */
+int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v,
+                                  float* out_w, float* out_u,
+                                  void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, qlka_stream_t stream,
+                                  float* sort_ms, float* walk_ms);
+
+/* ---- weighted abs sum, forward ---------------------------------------------------------
+ * out_w[p,m,c] = sum_{d,n} |k[p,d,n] - q[p,d,m]| v[p,n,c]           (P, M, C)
+ * out_u[p,m]   = sum_{d,n} |k[p,d,n] - q[p,d,m]|                    (P, M), optional (NULL)
+ * path: -1 auto, 0 global, 1 fused - kept for signature compatibility; the three values run
+ * the same kernels here, but path == 1 with max(N, M) > 4096 is rejected as in the reference.
+ * Replaces weighted_abs_sum_forward / weighted_abs_sum_full_forward,
+ * Weighted_Abs_Sum/csrc/binding.cpp:132-239. */
+int qlka_abs_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes);
+int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v,
+                                  float* out_w, float* out_u /* nullable */,
+                                  void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, int path, qlka_stream_t stream);
+
+/* ---- weighted abs sum, backward --------------------------------------------------------
+ * Gradients of sum(out_w * g_w) + sum(out_u * g_u) (g_u NULL: first term only):
+ * grad_q (P, D, M), grad_k (P, D, N), grad_v (P, N, C); a key equal to a query has
+ * sub-gradient -1 for both. Replaces weighted_abs_sum_backward /
+ * weighted_abs_sum_full_backward, Weighted_Abs_Sum/csrc/binding.cpp:246-380. */
+int qlka_abs_backward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes);
+int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* v,
+                                   const float* g_w, const float* g_u /* nullable */,
+                                   float* grad_q, float* grad_k, float* grad_v,
+                                   void* workspace, size_t workspace_bytes,
+                                   int P, int D, int N, int M, int C, qlka_stream_t stream);
+
+/* ---- weighted sgn sum ------------------------------------------------------------------
+ * out[p,d,m] = sum_n sgn(k[p,d,n] - q[p,d,m]) <v[p,n,:], g[p,m,:]>, sgn(0) = +1   (P, D, M)
+ * Replaces weighted_sgn_sum_forward, Weighted_Abs_Sum/csrc/binding.cpp:383-439. */
+int qlka_sgn_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes);
+int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v, const float* g,
+                                  float* out,
+                                  void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, qlka_stream_t stream);
+
+/* ---- diagnostic: the sort/rank stage alone ---------------------------------------------
+ * Sorts x (P, D, N) as the key stream and ranks y (P, D, M) against it, writing the walk
+ * records: xperm (P*D, NP) uint32, xval (P*D, NP + 8) float, yrec (P*D, M) 4 x uint32
+ * {e0, e1, row, rank}, mstart (P*D, MS) uint32, where NP = (N/8 + 1) * 8 and
+ * MS = (N/8 + 2) rounded up to a multiple of 4. mode 0: Laplace records, 1: abs records.
+ * Corresponds to sort_qk of the reference (Weighted_Laplace_Sum/csrc/binding.cpp:33-58);
+ * exists so that tests can check the stage on its own. */
+int qlka_sort_rank_workspace_bytes(int P, int D, int N, int M, size_t* bytes);
+int qlka_sort_rank_records(const float* x, const float* y,
+                           uint32_t* xperm, float* xval, uint32_t* yrec, uint32_t* mstart,
+                           void* workspace, size_t workspace_bytes,
+                           int P, int D, int N, int M, int mode, qlka_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QLKA_H */

@@ -1,0 +1,138 @@
+// Small streaming kernels around the walks: the pre-reductions and the rank-1 initial value
+// of the abs sum (the reference uses ATen sum / bmm for the former,
+// Weighted_Abs_Sum/csrc/binding.cpp:154-159,286-289,349-350, and abs_init for the latter,
+// Weighted_Abs_Sum/csrc/abs_kernels.cu:23-70), and channel padding to a multiple of four
+// (the reference pads odd C to even with constant_pad_nd, binding.cpp:87-89).
+#include "qlka_common.cuh"
+
+namespace qlka {
+
+// out[p, l] = sum_d x[p, d, l]
+__global__ void colsum_d_kernel(const float* __restrict__ x, float* __restrict__ out, const int D, const int L, const long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long p = i / L, l = i % L;
+    const float* src = x + p * D * L + l;
+    float acc = 0.0f;
+    for (int d = 0; d < D; d++) acc += src[(long long)d * L];
+    out[i] = acc;
+}
+
+// Per p over rows r of w (P, R, C4) with optional row scalars s (P, R):
+//   wsum[p, c] += sum_r w[r, c],  swsum[p, c] += sum_r s[r] w[r, c],  ssum[p] += sum_r s[r]
+// (outputs must be zeroed; partial sums of a row tile are added atomically). grid (tiles, P).
+constexpr int RS_THREADS = 256, RS_ROWS = 256;
+__global__ void __launch_bounds__(RS_THREADS) rowstat_kernel(
+    const float* __restrict__ w, const float* __restrict__ s,
+    float* __restrict__ wsum, float* __restrict__ swsum, float* __restrict__ ssum,
+    const int R, const int C4)
+{
+    __shared__ float red_w[RS_THREADS], red_k[RS_THREADS];
+    const int p  = blockIdx.y;
+    const int r0 = blockIdx.x * RS_ROWS, r1 = min(R, r0 + RS_ROWS);
+    const int CW = C4 <= 32 ? 32 : (C4 <= 64 ? 64 : 128);
+    const int c  = threadIdx.x % CW, lane_r = threadIdx.x / CW, nr = RS_THREADS / CW;
+    float aw = 0.0f, ak = 0.0f, as = 0.0f;
+    if (c < C4) {
+        for (int r = r0 + lane_r; r < r1; r += nr) {
+            const float x  = w[((long long)p * R + r) * C4 + c];
+            const float sc = s ? s[(long long)p * R + r] : 0.0f;
+            aw += x;
+            ak = fmaf(sc, x, ak);
+            if (c == 0) as += sc;
+        }
+    }
+    red_w[threadIdx.x] = aw; red_k[threadIdx.x] = ak;
+    __syncthreads();
+    if (lane_r == 0 && c < C4) {
+        for (int j = 1; j < nr; j++) { aw += red_w[j * CW + c]; ak += red_k[j * CW + c]; }
+        atomicAdd(wsum + (long long)p * C4 + c, aw);
+        if (swsum) atomicAdd(swsum + (long long)p * C4 + c, ak);
+    }
+    if (ssum && c == 0) atomicAdd(ssum + p, as);
+}
+
+// out[p] = sum_l x[p, l]; one CTA per p
+__global__ void __launch_bounds__(256) vecsum_kernel(const float* __restrict__ x, float* __restrict__ out, const int L) {
+    __shared__ float red[256];
+    const int p = blockIdx.x;
+    float acc = 0.0f;
+    for (int l = threadIdx.x; l < L; l += 256) acc += x[(long long)p * L + l];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int off = 128; off > 0; off >>= 1) {
+        if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out[p] = red[0];
+}
+
+// out[p, m, c] = ktot[p, c] - qsum[p, m] * vsum[p, c];  out_u[p, m] = ksr[p] - Nk * qsum[p, m]
+__global__ void abs_init_kernel(
+    const float* __restrict__ ktot, const float* __restrict__ vsum, const float* __restrict__ qsum,
+    const float* __restrict__ ksr, float* __restrict__ out, float* __restrict__ out_u,
+    const int M, const int C4, const float Nk, const long long total4)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    const int       q4 = C4 >> 2;
+    const int       c  = (int)(i % q4) * 4;
+    const long long pm = i / q4;
+    const long long p  = pm / M;
+    const float4 kt = *reinterpret_cast<const float4*>(ktot + p * C4 + c);
+    const float4 vs = *reinterpret_cast<const float4*>(vsum + p * C4 + c);
+    const float  qs = qsum[pm];
+    *reinterpret_cast<float4*>(out + pm * C4 + c) =
+        make_float4(fmaf(-qs, vs.x, kt.x), fmaf(-qs, vs.y, kt.y), fmaf(-qs, vs.z, kt.z), fmaf(-qs, vs.w, kt.w));
+    if (out_u && c == 0) out_u[pm] = ksr[p] - Nk * qs;
+}
+
+// dst (rows, C4) <- src (rows, C), zero filled
+__global__ void pad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, const int C, const int C4, const long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / C4; const int c = (int)(i % C4);
+    dst[i] = c < C ? src[r * C + c] : 0.0f;
+}
+// dst (rows, C) <- src (rows, C4)
+__global__ void unpad_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, const int C, const int C4, const long long total) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long r = i / C; const int c = (int)(i % C);
+    dst[i] = src[r * C4 + c];
+}
+
+static inline unsigned blocks_for(long long total, int threads) { return (unsigned)((total + threads - 1) / threads); }
+
+cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st) {
+    const long long total = (long long)P * L;
+    colsum_d_kernel<<<blocks_for(total, 256), 256, 0, st>>>(x, out, D, L, total);
+    return cudaGetLastError();
+}
+cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st) {
+    dim3 grid((R + RS_ROWS - 1) / RS_ROWS, P);
+    rowstat_kernel<<<grid, RS_THREADS, 0, st>>>(w, s, wsum, swsum, ssum, R, C4);
+    return cudaGetLastError();
+}
+cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t st) {
+    vecsum_kernel<<<P, 256, 0, st>>>(x, out, L);
+    return cudaGetLastError();
+}
+cudaError_t launch_abs_init(const float* ktot, const float* vsum, const float* qsum, const float* ksr,
+                            float* out, float* out_u, int P, int M, int C4, int Nk, cudaStream_t st) {
+    const long long total4 = (long long)P * M * (C4 >> 2);
+    abs_init_kernel<<<blocks_for(total4, 256), 256, 0, st>>>(ktot, vsum, qsum, ksr, out, out_u, M, C4, (float)Nk, total4);
+    return cudaGetLastError();
+}
+cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st) {
+    const long long total = rows * C4;
+    pad_rows_kernel<<<blocks_for(total, 256), 256, 0, st>>>(src, dst, C, C4, total);
+    return cudaGetLastError();
+}
+cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st) {
+    const long long total = rows * C;
+    unpad_rows_kernel<<<blocks_for(total, 256), 256, 0, st>>>(src, dst, C, C4, total);
+    return cudaGetLastError();
+}
+
+}  // namespace qlka

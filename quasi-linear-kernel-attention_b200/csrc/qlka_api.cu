@@ -1,0 +1,468 @@
+// Host side of the C ABI declared in include/qlka.h: argument checks that mirror the
+// reference's TORCH_CHECKs, workspace carving, launch plans, and the kernel sequences of the
+// four operators. No allocation, no synchronisation, no torch types.
+#include "../../include/qlka.h"
+#include "qlka_common.cuh"
+
+#include <climits>
+
+namespace qlka {
+cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
+cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream);
+cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
+int         walk_lanes_per_stream(int C4);
+cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st);
+cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st);
+cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t st);
+cudaError_t launch_abs_init(const float* ktot, const float* vsum, const float* qsum, const float* ksr,
+                            float* out, float* out_u, int P, int M, int C4, int Nk, cudaStream_t st);
+cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
+cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
+}  // namespace qlka
+
+using namespace qlka;
+
+namespace {
+
+thread_local int g_last_cuda = 0;
+
+constexpr int SMALL_MAX = 16384;     // longest segment the shared-memory sort handles
+constexpr int EMIT_ROWS = 0, EMIT_DOT = 1;
+
+#define CU(expr)                                                   \
+    do {                                                           \
+        cudaError_t e_ = (expr);                                   \
+        if (e_ != cudaSuccess) { g_last_cuda = (int)e_; return QLKA_ERR_CUDA; } \
+    } while (0)
+
+int check_dims(int P, int D, int N, int M, int C) {
+    if (P <= 0 || D <= 0 || N <= 0 || M <= 0) return QLKA_ERR_BAD_SHAPE;
+    if (C < 1 || C > 128) return QLKA_ERR_C_RANGE;
+    if (N > 131072 || M > 131072) return QLKA_ERR_LENGTH;
+    const long long mx = N > M ? N : M;
+    if ((long long)P * D * mx > (long long)INT_MAX) return QLKA_ERR_INT32;
+    if (mx > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;
+    return QLKA_OK;
+}
+
+// bump allocator over the workspace; with base == nullptr it only measures
+struct Bump {
+    char*  base;
+    size_t off = 0;
+    explicit Bump(void* b) : base(static_cast<char*>(b)) {}
+    template <class T> T* take(size_t n) {
+        off = (off + 255) & ~size_t(255);
+        T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+        off += n * sizeof(T);
+        return p;
+    }
+};
+
+int sm_count() {
+    static int cached = 0;
+    if (!cached) {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;                               // B200; also keeps workspace sizes defined without a device
+        cached = n;
+    }
+    return cached;
+}
+
+// how a walk over `nseg` segments of N keys is cut into streams, items and CTAs
+struct WalkPlan { int sps, segs, nitems, grid; };
+
+WalkPlan plan_walk(int nseg, int N, int C4) {
+    const int lps      = walk_lanes_per_stream(C4);
+    const int streams  = 256 / lps;
+    const int per_sm   = C4 <= 64 ? 2 : 1;
+    const int grid_cap = sm_count() * per_sm;
+    const int nbk      = nblocks(N);
+    int sps_max = 1;
+    while (sps_max * 2 <= streams && sps_max * 2 <= nbk) sps_max *= 2;
+    int sps = 1;
+    // more streams per segment until there are enough items to balance the persistent CTAs,
+    // but keep at least four key blocks per stream when the segment allows it
+    while (sps < sps_max && (long long)nseg * sps / streams < 8LL * grid_cap && nbk / (sps * 2) >= 4) sps *= 2;
+    WalkPlan w;
+    w.sps    = sps;
+    w.segs   = streams / sps;
+    w.nitems = (nseg + w.segs - 1) / w.segs;
+    w.grid   = w.nitems < grid_cap ? w.nitems : grid_cap;
+    return w;
+}
+
+// scratch of one sort/rank run over nseg segments of N keys and M queries
+struct Records {
+    uint32_t* xperm; float* xval; uint4* yrec; uint32_t* mstart; float* su0; float* su1;
+    void carve(Bump& b, int nseg, int N, int M) {
+        xperm  = b.take<uint32_t>((size_t)nseg * npad(N));
+        xval   = b.take<float>((size_t)nseg * xstride(N));
+        yrec   = b.take<uint4>((size_t)nseg * M);
+        mstart = b.take<uint32_t>((size_t)nseg * mstride(N));
+        su0    = b.take<float>((size_t)nseg * (N + 1));
+        su1    = b.take<float>((size_t)nseg * (N + 1));
+    }
+};
+
+SortArgs sort_args(const Records& r, const float* x, const float* y, int nseg, int D, int N, int M, int mode, int scal) {
+    SortArgs s{};
+    s.x = x; s.y = y;
+    s.xperm = r.xperm; s.xval = r.xval; s.yrec = r.yrec; s.mstart = r.mstart; s.su0 = r.su0; s.su1 = r.su1;
+    s.nseg = nseg; s.D = D; s.N = N; s.M = M; s.mode = mode; s.scal = scal;
+    return s;
+}
+
+WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int nseg, int D, int N, int M, int C4) {
+    WalkArgs a{};
+    a.rows = rows; a.xperm = r.xperm; a.xval = r.xval; a.yrec = r.yrec; a.mstart = r.mstart;
+    a.nseg = nseg; a.D = D; a.N = N; a.M = M; a.C4 = C4; a.sps = w.sps; a.nitems = w.nitems;
+    a.sign = 1.0f;
+    return a;
+}
+
+inline int round4(int C) { return (C + 3) & ~3; }
+
+bool ws_ok(const void* ws, size_t have, size_t need) {
+    return need == 0 || (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && have >= need);
+}
+
+// ------------------------------------------------------------------ Laplace forward
+struct LaplaceWs {
+    float* vpad; float* opad; Records rec; float* ckpt; float* wck; WalkPlan plan; size_t bytes;
+    LaplaceWs(void* base, int P, int D, int N, int M, int C) {
+        Bump b(base);
+        const int C4 = round4(C), nseg = P * D;
+        vpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        opad = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
+        rec.carve(b, nseg, N, M);
+        plan = plan_walk(nseg, N, C4);
+        ckpt = b.take<float>((size_t)plan.grid * plan.segs * nblocks(N) * C4);
+        wck  = b.take<float>((size_t)plan.grid * plan.segs * nblocks(N));
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+
+// ------------------------------------------------------------------ abs forward
+struct AbsFwdWs {
+    float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr; WalkPlan plan; size_t bytes;
+    AbsFwdWs(void* base, int P, int D, int N, int M, int C) {
+        Bump b(base);
+        const int C4 = round4(C), nseg = P * D;
+        vpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        opad = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
+        rec.carve(b, nseg, N, M);
+        qsum  = b.take<float>((size_t)P * M);
+        ksumd = b.take<float>((size_t)P * N);
+        vsum  = b.take<float>((size_t)P * C4 * 2 + P);     // vsum | ktot | ksr, zeroed together
+        ktot  = vsum ? vsum + (size_t)P * C4 : nullptr;
+        ksr   = vsum ? ktot + (size_t)P * C4 : nullptr;
+        plan  = plan_walk(nseg, N, C4);
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+
+// ------------------------------------------------------------------ abs backward / sgn
+struct AbsBwdWs {
+    float *vpad, *gpad, *gvpad; Records rec;
+    float *qsumd, *ksumd, *sums /* vsum | gwsum | qtotg | gu_total */;
+    size_t bytes;
+    AbsBwdWs(void* base, int P, int D, int N, int M, int C) {
+        Bump b(base);
+        const int C4 = round4(C), nseg = P * D;
+        vpad  = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        gpad  = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
+        gvpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        const int mx = N > M ? N : M;
+        rec.carve(b, nseg, mx, mx);
+        qsumd = b.take<float>((size_t)P * M);
+        ksumd = b.take<float>((size_t)P * N);
+        sums  = b.take<float>((size_t)P * C4 * 3 + P);
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+
+}  // namespace
+
+extern "C" {
+
+const char* qlka_status_string(int status) {
+    switch (status) {
+        case QLKA_OK:                    return "ok";
+        case QLKA_ERR_BAD_SHAPE:         return "N, M and D must be > 0";
+        case QLKA_ERR_C_RANGE:           return "C (v.size(2)) must be in [1, 128]";
+        case QLKA_ERR_LENGTH:            return "N and M must be <= 131072";
+        case QLKA_ERR_INT32:             return "P*D*max(N,M) must fit int32 (cub sort offsets)";
+        case QLKA_ERR_PATH:              return "path must be -1 (auto), 0 (global) or 1 (fused)";
+        case QLKA_ERR_FUSED_UNAVAILABLE: return "fused path pinned but unavailable: needs max(N,M) <= 4096 and the bucket's shared memory to fit this device";
+        case QLKA_ERR_NULL:              return "a required pointer is NULL";
+        case QLKA_ERR_WORKSPACE:         return "workspace too small or not 256-byte aligned";
+        case QLKA_ERR_CUDA:              return "a CUDA runtime call failed";
+        case QLKA_ERR_UNSUPPORTED:       return "no kernel in this build for max(N,M) > 16384";
+        default:                         return "unknown status";
+    }
+}
+
+int qlka_last_cuda_error(void) { return g_last_cuda; }
+
+// ---------------------------------------------------------------- Laplace
+int qlka_laplace_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    *bytes = LaplaceWs(nullptr, P, D, N, M, C).bytes;
+    return QLKA_OK;
+}
+
+static int laplace_forward_impl(const float* q, const float* k, const float* v,
+                                float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
+                                int P, int D, int N, int M, int C, cudaStream_t stream, cudaEvent_t* ev)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (!q || !k || !v || !out_w || !out_u) return QLKA_ERR_NULL;
+    LaplaceWs ws(workspace, P, D, N, M, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    const int C4 = round4(C), nseg = P * D;
+
+    const float* rows = v;
+    float*       out  = out_w;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        rows = ws.vpad; out = ws.opad;
+    }
+    CU(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)P * M * C4, stream));
+    CU(cudaMemsetAsync(out_u, 0, sizeof(float) * (size_t)P * M, stream));
+    if (ev) CU(cudaEventRecord(ev[0], stream));
+
+    SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_LAPLACE, SCAL_UNIT);
+    s.out_u = out_u;
+    CU(launch_sort_rank_small(s, stream));
+    if (ev) CU(cudaEventRecord(ev[1], stream));
+
+    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
+    w.ckpt = ws.ckpt; w.wck = ws.wck; w.out = out;
+    CU(launch_laplace_walk(w, ws.plan.grid, stream));
+    if (ev) CU(cudaEventRecord(ev[2], stream));
+
+    if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
+    return QLKA_OK;
+}
+
+int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const float* v,
+                                      float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
+                                      int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    return laplace_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C,
+                                reinterpret_cast<cudaStream_t>(stream_), nullptr);
+}
+
+int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v,
+                                  float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, qlka_stream_t stream_,
+                                  float* sort_ms, float* walk_ms)
+{
+    if (!sort_ms || !walk_ms) return QLKA_ERR_NULL;
+    cudaEvent_t ev[3];
+    for (int i = 0; i < 3; i++) CU(cudaEventCreate(&ev[i]));
+    int st = laplace_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C,
+                                  reinterpret_cast<cudaStream_t>(stream_), ev);
+    if (st == QLKA_OK) {
+        cudaError_t e = cudaEventSynchronize(ev[2]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(sort_ms, ev[0], ev[1]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(walk_ms, ev[1], ev[2]);
+        if (e != cudaSuccess) { g_last_cuda = (int)e; st = QLKA_ERR_CUDA; }
+    }
+    for (int i = 0; i < 3; i++) cudaEventDestroy(ev[i]);
+    return st;
+}
+
+// ---------------------------------------------------------------- abs forward
+int qlka_abs_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    *bytes = AbsFwdWs(nullptr, P, D, N, M, C).bytes;
+    return QLKA_OK;
+}
+
+int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v,
+                                  float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, int path, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (path < -1 || path > 1) return QLKA_ERR_PATH;
+    if (path == 1 && (N > 4096 || M > 4096)) return QLKA_ERR_FUSED_UNAVAILABLE;
+    if (!q || !k || !v || !out_w) return QLKA_ERR_NULL;
+    AbsFwdWs ws(workspace, P, D, N, M, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int C4 = round4(C), nseg = P * D;
+    const bool full = out_u != nullptr;
+
+    const float* rows = v;
+    float*       out  = out_w;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        rows = ws.vpad; out = ws.opad;
+    }
+    // rank-1 part: out = k_total - qsum * vsum, out_u = ksum_raw - N * qsum
+    CU(launch_colsum_d(q, ws.qsum, P, D, M, stream));
+    CU(launch_colsum_d(k, ws.ksumd, P, D, N, stream));
+    CU(cudaMemsetAsync(ws.vsum, 0, sizeof(float) * ((size_t)P * C4 * 2 + P), stream));
+    CU(launch_rowstat(rows, ws.ksumd, ws.vsum, ws.ktot, ws.ksr, P, N, C4, stream));
+    CU(launch_abs_init(ws.ktot, ws.vsum, ws.qsum, ws.ksr, out, out_u, P, M, C4, N, stream));
+
+    SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_ABS, full ? SCAL_UNIT : SCAL_NONE);
+    s.out_u = out_u;
+    CU(launch_sort_rank_small(s, stream));
+
+    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
+    w.out = out;
+    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid, stream));
+
+    if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
+    return QLKA_OK;
+}
+
+// ---------------------------------------------------------------- abs backward
+int qlka_abs_backward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    *bytes = AbsBwdWs(nullptr, P, D, N, M, C).bytes;
+    return QLKA_OK;
+}
+
+int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* v,
+                                   const float* g_w, const float* g_u,
+                                   float* grad_q, float* grad_k, float* grad_v,
+                                   void* workspace, size_t workspace_bytes,
+                                   int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (!q || !k || !v || !g_w || !grad_q || !grad_k || !grad_v) return QLKA_ERR_NULL;
+    AbsBwdWs ws(workspace, P, D, N, M, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int C4 = round4(C), nseg = P * D;
+    const bool full = g_u != nullptr;
+
+    const float* vrows = v;
+    const float* grows = g_w;
+    float*       gv    = grad_v;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        CU(launch_pad_rows(g_w, ws.gpad, (long long)P * M, C, C4, stream));
+        vrows = ws.vpad; grows = ws.gpad; gv = ws.gvpad;
+    }
+    float* vsum     = ws.sums;
+    float* gwsum    = vsum + (size_t)P * C4;
+    float* qtotg    = gwsum + (size_t)P * C4;
+    float* gu_total = qtotg + (size_t)P * C4;
+    CU(launch_colsum_d(q, ws.qsumd, P, D, M, stream));
+    CU(launch_colsum_d(k, ws.ksumd, P, D, N, stream));
+    CU(cudaMemsetAsync(ws.sums, 0, sizeof(float) * ((size_t)P * C4 * 3 + P), stream));
+    CU(launch_rowstat(vrows, nullptr, vsum, nullptr, nullptr, P, N, C4, stream));
+    CU(launch_rowstat(grows, ws.qsumd, gwsum, qtotg, nullptr, P, M, C4, stream));
+    if (full) CU(launch_vecsum(g_u, gu_total, P, M, stream));
+
+    {   // grad_q: queries q walk the key stream k; prefix of v rows contracted with g_w rows
+        SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, full ? SCAL_RANK : SCAL_NONE);
+        s.uq = g_u;
+        CU(launch_sort_rank_small(s, stream));
+        WalkPlan plan = plan_walk(nseg, N, C4);
+        WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
+        w.g = grows; w.wtotal = vsum; w.out_s = grad_q;
+        CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
+    }
+    {   // roles swapped: queries k walk the stream q whose rows are g_w
+        SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_ABS, full ? SCAL_PREFIX : SCAL_NONE);
+        s.us = g_u; s.us_total = gu_total;
+        CU(launch_sort_rank_small(s, stream));
+        WalkPlan plan = plan_walk(nseg, M, C4);
+        // grad_k: prefix of g_w rows contracted with v rows (+ the g_u prefix term carried in e1)
+        WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
+        w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k;
+        CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
+        // grad_v: abs sum with keys q, weights g_w, evaluated at the keys k
+        CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, stream));
+        WalkArgs w2 = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
+        w2.out = gv;
+        CU(launch_prefix_walk(w2, EMIT_ROWS, plan.grid, stream));
+    }
+    if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
+    return QLKA_OK;
+}
+
+// ---------------------------------------------------------------- sgn
+int qlka_sgn_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes) {
+    return qlka_abs_backward_workspace_bytes(P, D, N, M, C, bytes);
+}
+
+int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v, const float* g,
+                                  float* out, void* workspace, size_t workspace_bytes,
+                                  int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (!q || !k || !v || !g || !out) return QLKA_ERR_NULL;
+    AbsBwdWs ws(workspace, P, D, N, M, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int C4 = round4(C), nseg = P * D;
+
+    const float* vrows = v;
+    const float* grows = g;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        CU(launch_pad_rows(g, ws.gpad, (long long)P * M, C, C4, stream));
+        vrows = ws.vpad; grows = ws.gpad;
+    }
+    float* vsum = ws.sums;
+    CU(cudaMemsetAsync(vsum, 0, sizeof(float) * (size_t)P * C4, stream));
+    CU(launch_rowstat(vrows, nullptr, vsum, nullptr, nullptr, P, N, C4, stream));
+
+    SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, SCAL_NONE);
+    CU(launch_sort_rank_small(s, stream));
+    WalkPlan plan = plan_walk(nseg, N, C4);
+    WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
+    w.g = grows; w.wtotal = vsum; w.out_s = out; w.sign = -1.0f;
+    CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
+    return QLKA_OK;
+}
+
+// ---------------------------------------------------------------- diagnostic
+int qlka_sort_rank_workspace_bytes(int P, int D, int N, int M, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = check_dims(P, D, N, M, 1);
+    if (st) return st;
+    *bytes = sizeof(float) * 2 * (size_t)P * D * (N + 1) + 512;
+    return QLKA_OK;
+}
+
+int qlka_sort_rank_records(const float* x, const float* y,
+                           uint32_t* xperm, float* xval, uint32_t* yrec, uint32_t* mstart,
+                           void* workspace, size_t workspace_bytes,
+                           int P, int D, int N, int M, int mode, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, 1);
+    if (st) return st;
+    if (!x || !y || !xperm || !xval || !yrec || !mstart) return QLKA_ERR_NULL;
+    if (mode != MODE_LAPLACE && mode != MODE_ABS) return QLKA_ERR_PATH;
+    size_t need = 0;
+    qlka_sort_rank_workspace_bytes(P, D, N, M, &need);
+    if (!ws_ok(workspace, workspace_bytes, need)) return QLKA_ERR_WORKSPACE;
+    Bump b(workspace);
+    Records r;
+    r.xperm = xperm; r.xval = xval; r.yrec = reinterpret_cast<uint4*>(yrec); r.mstart = mstart;
+    r.su0 = b.take<float>((size_t)P * D * (N + 1));
+    r.su1 = b.take<float>((size_t)P * D * (N + 1));
+    SortArgs s = sort_args(r, x, y, P * D, D, N, M, mode, SCAL_NONE);
+    CU(launch_sort_rank_small(s, reinterpret_cast<cudaStream_t>(stream_)));
+    return QLKA_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,88 @@
+// Shared definitions of the sorted-walk kernels (sm_100a).
+//
+// One "segment" is one (p = batch*head, d = feature dimension) pair: a stream of N sorted
+// keys, each pointing at a row of C channels, and M queries that are merged into it.
+// The sort/rank kernel turns a segment into four arrays ("walk records") in scratch
+// memory; the walk kernels consume only those, never the raw keys:
+//
+//   xperm [seg][NP]        uint32  row index of the j-th smallest key (0 for j >= N)
+//   xval  [seg][NP + KB]   float   per-key scalar: the step decay exp(-(k_j - k_{j-1}))
+//                                  (Laplace, 0 for j = 0, 1 for j >= N) or the key value (abs)
+//   yrec  [seg][M]         uint4   per query in ascending order: {e0, e1, row, rank}, rank =
+//                                  number of keys strictly below the query (ties count above)
+//   mstart[seg][NBK + 1]   uint32  first query whose rank is >= b*KB, for every key block b
+//
+// with KB = 8 keys per block, NBK = N/KB + 1 blocks and NP = NBK*KB padded keys, so that at
+// least one padded position follows the last key and every rank in [0, N] falls in a block.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace qlka {
+
+constexpr int KB = 8;                       // keys per block of the walk
+constexpr unsigned FULL = 0xffffffffu;
+
+__host__ __device__ inline int       nblocks(int N)  { return N / KB + 1; }
+__host__ __device__ inline int       npad(int N)     { return nblocks(N) * KB; }
+__host__ __device__ inline long long xstride(int N)  { return (long long)npad(N) + KB; }
+__host__ __device__ inline long long mstride(int N)  { return (long long)((nblocks(N) + 1 + 3) & ~3); }
+
+enum SortMode : int { MODE_LAPLACE = 0, MODE_ABS = 1, MODE_SGN = 2 };
+// scalar side channel of the sort/rank kernel
+enum ScalMode : int {
+    SCAL_NONE = 0,
+    SCAL_UNIT = 1,      // accumulate the v == 1 column of the sum into out_u[p, row]
+    SCAL_RANK = 2,      // e1 = uq[p, row] * (2 rank - N)
+    SCAL_PREFIX = 3     // e1 = 2 * (sum of us over keys below) - us_total[p]
+};
+
+struct SortArgs {
+    const float* x;          // (P, D, N) keys to sort into the stream
+    const float* y;          // (P, D, M) queries
+    uint32_t*    xperm;
+    float*       xval;
+    uint4*       yrec;
+    uint32_t*    mstart;
+    float*       su0;        // [seg][N + 1] scratch for the scalar scans
+    float*       su1;
+    float*       out_u;      // (P, M)  SCAL_UNIT
+    const float* uq;         // (P, M)  SCAL_RANK
+    const float* us;         // (P, N)  SCAL_PREFIX
+    const float* us_total;   // (P)     SCAL_PREFIX
+    int nseg, D, N, M, mode, scal;
+};
+
+struct WalkArgs {
+    const float*    rows;     // (P, N, C4) rows the stream points at
+    const uint32_t* xperm;
+    const float*    xval;
+    const uint4*    yrec;
+    const uint32_t* mstart;
+    float*          ckpt;     // Laplace: [cta slot][NBK][C4] suffix checkpoints
+    float*          wck;      // Laplace: [cta slot][NBK]
+    float*          out;      // emit rows: (P, M, C4), accumulated with vector reductions
+    const float*    g;        // emit dot: (P, M, C4) matrix contracted with the prefix
+    const float*    wtotal;   // emit dot: (P, C4) column sums of rows
+    float*          out_s;    // emit dot: (P, D, M) plain stores
+    float           sign;     // emit dot: output scale (+1 gradients, -1 public sgn op)
+    int nseg, D, N, M, C4, sps, nitems;
+};
+
+__device__ __forceinline__ uint32_t f2key(float f) {
+    uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key2f(uint32_t u) {
+    return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
+}
+
+// 16-byte vector reduction into global memory (no return value)
+__device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ float4 ldg4(const float* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
+
+}  // namespace qlka

@@ -1,0 +1,208 @@
+"""ctypes binding of libqlka.so (the C ABI of include/qlka.h) for torch tensors.
+
+torch is used for device memory and the current stream only; the kernels are the
+library's. There is no fallback: a missing library or a non-CUDA tensor raises.
+The tensor checks and their messages follow the reference's host code
+(Weighted_Laplace_Sum/csrc/binding.cpp:66-79, Weighted_Abs_Sum/csrc/binding.cpp:69-84,
+:251-262, :387-392).
+"""
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libqlka.so")
+_lib = None
+
+_vp, _sz, _i = ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int
+
+
+def lib():
+    """The loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}` "
+                "(nvcc, sm_100a). There is no CPU or PyTorch fallback for these operators.")
+        L = ctypes.CDLL(LIB_PATH)
+        L.qlka_status_string.restype = ctypes.c_char_p
+        L.qlka_status_string.argtypes = [_i]
+        L.qlka_last_cuda_error.restype = _i
+        for name in ("laplace_forward", "abs_forward", "abs_backward", "sgn_forward"):
+            f = getattr(L, f"qlka_{name}_workspace_bytes")
+            f.restype, f.argtypes = _i, [_i] * 5 + [ctypes.POINTER(_sz)]
+        L.qlka_sort_rank_workspace_bytes.restype = _i
+        L.qlka_sort_rank_workspace_bytes.argtypes = [_i] * 4 + [ctypes.POINTER(_sz)]
+        L.qlka_weighted_laplace_sum_forward.restype = _i
+        L.qlka_weighted_laplace_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp]
+        L.qlka_laplace_forward_stage_ms.restype = _i
+        L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 2
+        L.qlka_weighted_abs_sum_forward.restype = _i
+        L.qlka_weighted_abs_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 6 + [_vp]
+        L.qlka_weighted_abs_sum_backward.restype = _i
+        L.qlka_weighted_abs_sum_backward.argtypes = [_vp] * 8 + [_vp, _sz] + [_i] * 5 + [_vp]
+        L.qlka_weighted_sgn_sum_forward.restype = _i
+        L.qlka_weighted_sgn_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp]
+        L.qlka_sort_rank_records.restype = _i
+        L.qlka_sort_rank_records.argtypes = [_vp] * 6 + [_vp, _sz] + [_i] * 5 + [_vp]
+        _lib = L
+    return _lib
+
+
+def _raise(status):
+    L = lib()
+    msg = L.qlka_status_string(status).decode()
+    if status == 9:
+        msg += f" (cudaError {L.qlka_last_cuda_error()})"
+    raise RuntimeError(msg)
+
+
+def _check(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def check_qkv(q, k, v, names="q, k and v"):
+    _check(q.is_cuda and k.is_cuda and v.is_cuda, f"{names} must be CUDA tensors")
+    _check(q.device == k.device == v.device, f"{names} must be on one device")
+    _check(q.dtype == k.dtype == v.dtype == torch.float32, f"{names} must be float32")
+    _check(q.dim() == 3 and k.dim() == 3 and v.dim() == 3, f"{names} must be 3D")
+    _check(q.size(0) == k.size(0) == v.size(0), "batch size must match")
+    _check(q.size(1) == k.size(1), "q and k must have the same feature dimension")
+    _check(k.size(2) == v.size(1), "k and v must have the same length")
+    _check(q.is_contiguous() and k.is_contiguous() and v.is_contiguous(), f"{names} must be contiguous")
+    return q.size(0), q.size(1), k.size(2), q.size(2), v.size(2)      # P, D, N, M, C
+
+
+def _check_like(t, name, shape, ref):
+    _check(t.is_cuda and t.device == ref.device, f"{name} must be on q's CUDA device")
+    _check(t.dtype == torch.float32, f"{name} must be float32")
+    _check(tuple(t.shape) == tuple(shape), f"{name} must have shape {tuple(shape)}")
+    _check(t.is_contiguous(), f"{name} must be contiguous")
+
+
+def _workspace(fn, dims, device):
+    n = _sz(0)
+    st = fn(*dims, ctypes.byref(n))
+    if st:
+        _raise(st)
+    return torch.empty(max(int(n.value), 256), dtype=torch.uint8, device=device), int(n.value)
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def laplace_forward(q, k, v):
+    P, D, N, M, C = dims = check_qkv(q, k, v)
+    L = lib()
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_laplace_forward_workspace_bytes, dims, q.device)
+        out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
+        out_u = torch.empty(P, M, dtype=torch.float32, device=q.device)
+        st = L.qlka_weighted_laplace_sum_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(), out_u.data_ptr(),
+                                                 ws.data_ptr(), n, P, D, N, M, C, _stream())
+    if st:
+        _raise(st)
+    return out_w, out_u
+
+
+def laplace_stage_times(q, k, v, reps=5):
+    """Diagnostic: median device time (ms) of the sort/rank kernel and of the walk kernel."""
+    P, D, N, M, C = dims = check_qkv(q, k, v)
+    L = lib()
+    sort_ms, walk_ms = [], []
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_laplace_forward_workspace_bytes, dims, q.device)
+        out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
+        out_u = torch.empty(P, M, dtype=torch.float32, device=q.device)
+        for _ in range(reps):
+            a, b = ctypes.c_float(0), ctypes.c_float(0)
+            st = L.qlka_laplace_forward_stage_ms(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(), out_u.data_ptr(),
+                                                 ws.data_ptr(), n, P, D, N, M, C, _stream(), ctypes.byref(a), ctypes.byref(b))
+            if st:
+                _raise(st)
+            sort_ms.append(a.value)
+            walk_ms.append(b.value)
+    sort_ms.sort()
+    walk_ms.sort()
+    return {"sort_rank_ms": sort_ms[len(sort_ms) // 2], "walk_ms": walk_ms[len(walk_ms) // 2]}
+
+
+def abs_forward(q, k, v, full, path=-1):
+    P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
+    L = lib()
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_abs_forward_workspace_bytes, dims, q.device)
+        out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
+        out_u = torch.empty(P, M, dtype=torch.float32, device=q.device) if full else None
+        st = L.qlka_weighted_abs_sum_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(),
+                                             out_u.data_ptr() if full else None,
+                                             ws.data_ptr(), n, P, D, N, M, C, int(path), _stream())
+    if st:
+        _raise(st)
+    return out_w, out_u
+
+
+def abs_backward(q, k, v, g_w, g_u=None):
+    P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
+    _check_like(g_w, "g_w", (P, M, C), q)
+    if g_u is not None:
+        _check_like(g_u, "g_u", (P, M), q)
+    L = lib()
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_abs_backward_workspace_bytes, dims, q.device)
+        gq = torch.empty(P, D, M, dtype=torch.float32, device=q.device)
+        gk = torch.empty(P, D, N, dtype=torch.float32, device=q.device)
+        gv = torch.empty(P, N, C, dtype=torch.float32, device=q.device)
+        st = L.qlka_weighted_abs_sum_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(), g_w.data_ptr(),
+                                              None if g_u is None else g_u.data_ptr(),
+                                              gq.data_ptr(), gk.data_ptr(), gv.data_ptr(),
+                                              ws.data_ptr(), n, P, D, N, M, C, _stream())
+    if st:
+        _raise(st)
+    return gq, gk, gv
+
+
+def sgn_forward(q, k, v, g):
+    P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
+    _check_like(g, "g", (P, M, C), q)
+    L = lib()
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_sgn_forward_workspace_bytes, dims, q.device)
+        out = torch.empty(P, D, M, dtype=torch.float32, device=q.device)
+        st = L.qlka_weighted_sgn_sum_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), out.data_ptr(),
+                                             ws.data_ptr(), n, P, D, N, M, C, _stream())
+    if st:
+        _raise(st)
+    return out
+
+
+def sort_rank_records(x, y, mode):
+    """Diagnostic: the walk records of the sort/rank stage (see include/qlka.h)."""
+    _check(x.is_cuda and y.is_cuda and x.dtype == y.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous(),
+           "x and y must be contiguous float32 CUDA tensors")
+    P, D, N = x.shape
+    M = y.shape[2]
+    L = lib()
+    NBK = N // 8 + 1
+    NP, MS = NBK * 8, (NBK + 1 + 3) // 4 * 4
+    dev = x.device
+    with torch.cuda.device(dev):
+        n = _sz(0)
+        st = L.qlka_sort_rank_workspace_bytes(P, D, N, M, ctypes.byref(n))
+        if st:
+            _raise(st)
+        ws = torch.empty(int(n.value), dtype=torch.uint8, device=dev)
+        xperm = torch.zeros(P * D, NP, dtype=torch.int32, device=dev)
+        xval = torch.zeros(P * D, NP + 8, dtype=torch.float32, device=dev)
+        yrec = torch.zeros(P * D, M, 4, dtype=torch.int32, device=dev)
+        mstart = torch.zeros(P * D, MS, dtype=torch.int32, device=dev)
+        st = L.qlka_sort_rank_records(x.data_ptr(), y.data_ptr(), xperm.data_ptr(), xval.data_ptr(), yrec.data_ptr(),
+                                      mstart.data_ptr(), ws.data_ptr(), int(n.value), P, D, N, M, int(mode), _stream())
+    if st:
+        _raise(st)
+    return xperm, xval, yrec, mstart

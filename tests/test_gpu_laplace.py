@@ -1,0 +1,104 @@
+"""weighted_laplace_sum on the GPU (through the C ABI) against the CPU checkers."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import direct, sorted_scan
+from util import make_inputs, rel_err
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4          # max|a-b| / max|b| against float64; the north-star bound is 1e-3
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+SHAPES = [
+    (1, 1, 1, 1, 1), (2, 3, 7, 5, 4), (1, 2, 8, 9, 3), (2, 4, 100, 77, 32), (1, 3, 257, 300, 33),
+    (1, 2, 64, 1000, 64), (1, 2, 1000, 3, 65), (2, 2, 600, 600, 64), (1, 2, 1024, 1024, 128),
+    (1, 3, 2049, 1500, 16), (1, 2, 4096, 4096, 64), (3, 2, 5000, 7000, 8), (1, 2, 16384, 16384, 64),
+]
+
+
+@pytest.mark.parametrize("shape", SHAPES)
+def test_forward_matches_oracle(shape):
+    from weighted_laplace_sum import weighted_laplace_sum
+    P, D, N, M, C = shape
+    q, k, v = make_inputs(P, D, N, M, C, seed=N + M + C, scale=2.0)
+    out_w, out_u = weighted_laplace_sum(q, k, v)
+    torch.cuda.synchronize()
+    ref_w, ref_u = sorted_scan.laplace_sum(q, k, v)
+    assert out_w.shape == (P, M, C) and out_u.shape == (P, M)
+    assert rel_err(out_w, ref_w) < TOL, f"out_w rel err {rel_err(out_w, ref_w)}"
+    assert rel_err(out_u, ref_u) < TOL, f"out_u rel err {rel_err(out_u, ref_u)}"
+    if N * M * D * P <= 1 << 24:
+        dw, du = direct.laplace_sum(q, k, v)
+        assert rel_err(out_w, dw) < TOL and rel_err(out_u, du) < TOL
+
+
+def test_two_calls_agree_and_inputs_untouched():
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs(2, 4, 3000, 2500, 64, seed=5)
+    q0, k0, v0 = q.clone(), k.clone(), v.clone()
+    a = weighted_laplace_sum(q, k, v)
+    b = weighted_laplace_sum(q, k, v)
+    torch.cuda.synchronize()
+    assert torch.equal(q, q0) and torch.equal(k, k0) and torch.equal(v, v0)
+    assert rel_err(a[0], b[0].double()) < 1e-5 and rel_err(a[1], b[1].double()) < 1e-5     # atomics: order differs
+
+
+def test_far_apart_keys_do_not_overflow():
+    """Keys hundreds of units below every query: all exponent arguments stay <= 0."""
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs(1, 2, 300, 200, 8, seed=9, ties=False)
+    k[0, 0, :50] -= 500.0
+    q[0, 1, :20] += 300.0
+    out_w, out_u = weighted_laplace_sum(q, k, v)
+    ref_w, ref_u = sorted_scan.laplace_sum(q, k, v)
+    assert torch.isfinite(out_w).all() and torch.isfinite(out_u).all()
+    assert rel_err(out_w, ref_w) < TOL and rel_err(out_u, ref_u) < TOL
+
+
+def test_config1_against_reference_golden():
+    """B=1,H=4,N=1024,D=Dv=32 add_laplace attention against the reference's own output."""
+    from kernel_attention import attention
+    z = np.load(os.path.join(GOLD, "c1_add_laplace.npz"))
+    q, k, v = (torch.from_numpy(z[n]).cuda() for n in ("q", "k", "v"))
+    out = attention(q, k, v, "add_laplace", float(z["tau"]))
+    assert rel_err(out, torch.from_numpy(z["naive"])) < TOL
+    assert rel_err(out, torch.from_numpy(z["chunked"])) < TOL
+
+
+def test_linearity_and_sampled_head_at_full_size():
+    """B=4,H=12,N=16384,D=Dv=64 is too big for the checker as a whole: one head goes through the
+    C restatement, and the full batch is checked through linearity in v."""
+    from weighted_laplace_sum import weighted_laplace_sum
+    P, D, N, C = 48, 64, 16384, 64
+    g = torch.Generator().manual_seed(0)
+    q = (torch.randn(P, D, N, generator=g) * 2).cuda()
+    k = (torch.randn(P, D, N, generator=g) * 2).cuda()
+    v1 = torch.randn(P, N, C, generator=g).cuda()
+    v2 = torch.randn(P, N, C, generator=g).cuda()
+    w1, u1 = weighted_laplace_sum(q, k, v1)
+    w2, u2 = weighted_laplace_sum(q, k, v2)
+    w3, u3 = weighted_laplace_sum(q, k, 2.0 * v1 - 0.5 * v2)
+    assert rel_err(w3, (2.0 * w1.double() - 0.5 * w2.double())) < TOL
+    assert rel_err(u3, u1.double()) < 1e-5
+    p = 17
+    ref_w, ref_u = sorted_scan.laplace_sum(q[p:p + 1], k[p:p + 1], v1[p:p + 1])
+    assert rel_err(w1[p:p + 1], ref_w) < TOL and rel_err(u1[p:p + 1], ref_u) < TOL
+
+
+def test_argument_errors():
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs(1, 2, 16, 16, 4, seed=1)
+    with pytest.raises(RuntimeError, match="CUDA tensors"):
+        weighted_laplace_sum(q.cpu(), k, v)
+    with pytest.raises(RuntimeError, match="float32"):
+        weighted_laplace_sum(q.double(), k.double(), v.double())
+    with pytest.raises(RuntimeError, match="contiguous"):
+        weighted_laplace_sum(q.transpose(1, 2).contiguous().transpose(1, 2), k, v)
+    with pytest.raises(RuntimeError, match="same length"):
+        weighted_laplace_sum(q, k, v[:, :8])
+    with pytest.raises(RuntimeError, match=r"\[1, 128\]"):
+        weighted_laplace_sum(q, k, torch.zeros(1, 16, 129, device="cuda"))

@@ -173,14 +173,16 @@ def run_ours(args, rank, world, local_rank):
         out_w_h.copy_(ow, non_blocking=True)
         out_u_h.copy_(ou, non_blocking=True)
 
-    e2e_step()
-    barrier()
-    e0.record()
-    for _ in range(n_e2e):
+    ms_e2e = float("nan")
+    if not args.no_e2e:
         e2e_step()
-    e1.record()
-    barrier()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
+        barrier()
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms_e2e = max_over_ranks(e0.elapsed_time(e1)) / n_e2e
 
     if rank != 0:
         return
@@ -209,13 +211,21 @@ def run_ours(args, rank, world, local_rank):
 
 
 def main():
+    global B, P, WORKLOAD, ALGO_BYTES
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--batch", type=int, default=B, help="B of the workload (default: the benchmark's 4; smaller for profiler captures)")
     args = ap.parse_args()
+    if args.batch != B:
+        B = args.batch
+        P = B * H
+        WORKLOAD = WORKLOAD.replace("B=4", f"B={B}")
+        ALGO_BYTES = 4 * P * (D * N + D * N + N * C + N * C + N)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

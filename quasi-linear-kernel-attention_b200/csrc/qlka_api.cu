@@ -121,7 +121,9 @@ WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int n
     return a;
 }
 
-inline int round4(int C) { return (C + 3) & ~3; }
+// channels as the kernels see them: padded to the lane granularity of the walk (4 floats up to 64
+// channels, 8 floats above, where a lane owns 8 channels)
+inline int round4(int C) { return C <= 64 ? (C + 3) & ~3 : (C + 7) & ~7; }
 
 bool ws_ok(const void* ws, size_t have, size_t need) {
     return need == 0 || (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && have >= need);

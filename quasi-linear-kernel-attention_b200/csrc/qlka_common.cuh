@@ -54,7 +54,7 @@ struct SortArgs {
 };
 
 struct WalkArgs {
-    const float*    rows;     // (P, N, C4) rows the stream points at
+    const float*    rows;     // (P, N, C4) rows the stream points at; C4 = channels padded to 4 (<= 64) or 8 floats
     const uint32_t* xperm;
     const float*    xval;
     const uint4*    yrec;

@@ -7,7 +7,7 @@ def rel_err(a, b):
     """max|a - b| / max|b| with b the checker's float64 result."""
     a = a.detach().to(torch.float64).cpu()
     b = b.detach().to(torch.float64).cpu()
-    return ((a - b).abs().max() / b.abs().max().clamp_min(1e-30)).item()
+    return ((a - b).abs().max() / b.abs().max().clamp_min(1e-6)).item()
 
 
 def make_inputs(P, D, N, M, C, seed, scale=1.0, ties=True, device="cuda"):
@@ -15,7 +15,7 @@ def make_inputs(P, D, N, M, C, seed, scale=1.0, ties=True, device="cuda"):
     q = torch.randn(P, D, M, generator=g) * scale
     k = torch.randn(P, D, N, generator=g) * scale
     v = torch.randn(P, N, C, generator=g)
-    if ties:
+    if ties and N * M > 1:            # (a lone key equal to the lone query makes the abs sum exactly 0)
         n = min(N, M, 5)
         k[0, 0, :n] = q[0, 0, :n]                 # keys equal to queries
         if N > 3:

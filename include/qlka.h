@@ -102,8 +102,8 @@ int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v
 
 /* ---- diagnostic: the sort/rank stage alone ---------------------------------------------
  * Sorts x (P, D, N) as the key stream and ranks y (P, D, M) against it, writing the walk
- * records: xperm (P*D, NP) uint32, xval (P*D, NP + 8) float, yrec (P*D, M) 4 x uint32
- * {e0, e1, row, rank}, mstart (P*D, MS) uint32, where NP = (N/8 + 1) * 8 and
+ * records: xperm (P*D, NP) uint32, xval (P*D, NP + 8) float, yrec (P*D, M + 1) 4 x uint32
+ * {e0, e1, row, rank} (the last entry of a segment is a sentinel), mstart (P*D, MS) uint32, where NP = (N/8 + 1) * 8 and
  * MS = (N/8 + 2) rounded up to a multiple of 4. mode 0: Laplace records, 1: abs records.
  * Corresponds to sort_qk of the reference (Weighted_Laplace_Sum/csrc/binding.cpp:33-58);
  * exists so that tests can check the stage on its own. */

@@ -98,7 +98,7 @@ struct Records {
     void carve(Bump& b, int nseg, int N, int M) {
         xperm  = b.take<uint32_t>((size_t)nseg * npad(N));
         xval   = b.take<float>((size_t)nseg * xstride(N));
-        yrec   = b.take<uint4>((size_t)nseg * M);
+        yrec   = b.take<uint4>((size_t)nseg * (M + 1));
         mstart = b.take<uint32_t>((size_t)nseg * mstride(N));
         su0    = b.take<float>((size_t)nseg * (N + 1));
         su1    = b.take<float>((size_t)nseg * (N + 1));

@@ -8,8 +8,9 @@
 //   xperm [seg][NP]        uint32  row index of the j-th smallest key (0 for j >= N)
 //   xval  [seg][NP + KB]   float   per-key scalar: the step decay exp(-(k_j - k_{j-1}))
 //                                  (Laplace, 0 for j = 0, 1 for j >= N) or the key value (abs)
-//   yrec  [seg][M]         uint4   per query in ascending order: {e0, e1, row, rank}, rank =
-//                                  number of keys strictly below the query (ties count above)
+//   yrec  [seg][M + 1]     uint4   per query in ascending order: {e0, e1, row, rank}, rank =
+//                                  number of keys strictly below the query (ties count above);
+//                                  entry M is a sentinel with rank 0xffffffff
 //   mstart[seg][NBK + 1]   uint32  first query whose rank is >= b*KB, for every key block b
 //
 // with KB = 8 keys per block, NBK = N/KB + 1 blocks and NP = NBK*KB padded keys, so that at

@@ -170,7 +170,7 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
 
     uint32_t* xperm  = a.xperm + (long long)seg * NP;
     float*    xval   = a.xval + (long long)seg * xstride(N);
-    uint4*    yrec   = a.yrec + (long long)seg * M;
+    uint4*    yrec   = a.yrec + (long long)seg * (M + 1);
     uint32_t* mstart = a.mstart + (long long)seg * mstride(N);
     float*    su0    = a.su0 ? a.su0 + (long long)seg * (N + 1) : nullptr;
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
         yrec[m] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), row, (uint32_t)r);
         skey[m] = (uint32_t)r;                    // only this thread ever reads skey[m] above
     }
+    if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
     __syncthreads();
     for (int b = tid; b <= NBK; b += THREADS)
         mstart[b] = b == NBK ? (uint32_t)M : (uint32_t)lower_bound_u(skey, M, (uint32_t)(b * KB));

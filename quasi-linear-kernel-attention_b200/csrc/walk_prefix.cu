@@ -9,35 +9,24 @@
 //              (Weighted_Abs_Sum/csrc/sgn_kernels.cu:8-15, sgn_prefix :17-192); one writer per
 //              output element, plain stores.
 //
-// Same thread mapping as the Laplace walk (LPS lanes per stream, CPL channels per lane,
-// SPS streams per segment, persistent CTAs). Pass 1 sums each stream's rows, a shared-memory
-// scan turns the sums into each stream's incoming prefix, pass 2 walks forward and emits.
-// With one stream per segment pass 1 and the scan are skipped.
-#include "qlka_common.cuh"
+// Same thread mapping and row staging as the Laplace walk (LPS lanes per stream, CPL channels
+// per lane, SPS streams per segment, persistent CTAs, cp.async ring). Pass 1 sums each
+// stream's rows, a shared-memory scan turns the sums into each stream's incoming prefix,
+// pass 2 walks forward and emits. With one stream per segment pass 1 and the scan are skipped.
+#include "walk_ring.cuh"
 
 namespace qlka {
 
-constexpr int PWALK_THREADS = 256;
 enum { EMIT_ROWS = 0, EMIT_DOT = 1 };
 
-template <int CPL>
-struct PVec { float x[CPL]; };
-
-template <int CPL>
-__device__ __forceinline__ void pload_row(PVec<CPL>& r, const float* __restrict__ p, const bool on) {
-    #pragma unroll
-    for (int c = 0; c < CPL; c += 4) {
-        float4 t = on ? ldg4(p + c) : make_float4(0.f, 0.f, 0.f, 0.f);
-        r.x[c] = t.x; r.x[c + 1] = t.y; r.x[c + 2] = t.z; r.x[c + 3] = t.w;
-    }
-}
-
 template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(PWALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(const WalkArgs a)
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(const WalkArgs a)
 {
-    constexpr int  STREAMS = PWALK_THREADS / LPS;
+    constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr int  CW      = LPS * CPL;
     constexpr bool WITH_K  = EMIT == EMIT_ROWS;
+    extern __shared__ __align__(16) float4 ring[];
+    __shared__ __align__(16) float sx[STREAMS][RING_DEPTH][SX_STRIDE];
     __shared__ float sV[STREAMS][CW];
     __shared__ float sK[WITH_K ? STREAMS : 1][WITH_K ? CW : 1];
 
@@ -48,46 +37,49 @@ __global__ void __launch_bounds__(PWALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk
     const int N = a.N, M = a.M, C4 = a.C4;
     const int NBK = nblocks(N), NP = npad(N);
     const bool lane_on = c0 < C4;
+    const int  c0l     = lane_on ? c0 : 0;
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
 
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
         const bool seg_on = seg < a.nseg;
         const bool on     = seg_on && lane_on;
-        const int  p      = seg_on ? seg / a.D : 0;
+        const int  sg     = seg_on ? seg : 0;
+        const int  p      = sg / a.D;
         const int  b0     = seg_on ? (int)((long long)s * NBK / SPS) : 0;
         const int  b1     = seg_on ? (int)((long long)(s + 1) * NBK / SPS) : 0;
+        const int  nblk   = b1 - b0;
 
-        const uint32_t* xperm  = a.xperm + (long long)(seg_on ? seg : 0) * NP;
-        const float*    xval   = WITH_K ? a.xval + (long long)(seg_on ? seg : 0) * xstride(N) : nullptr;
-        const uint4*    yrec   = a.yrec + (long long)(seg_on ? seg : 0) * M;
-        const uint32_t* mstart = a.mstart + (long long)(seg_on ? seg : 0) * mstride(N);
-        const float*    rows   = a.rows + (long long)p * N * C4 + c0;
+        const uint32_t* xperm = a.xperm + (long long)sg * NP;
+        const float*    xval  = WITH_K ? a.xval + (long long)sg * xstride(N) : nullptr;
+        const float*    rows  = a.rows + (long long)p * N * C4 + c0l;
 
-        PVec<CPL> PV, PK;
-        #pragma unroll
-        for (int c = 0; c < CPL; c++) { PV.x[c] = 0.0f; PK.x[c] = 0.0f; }
+        Vec<CPL> PV, PK;
+        PV.zero(); PK.zero();
 
         if (SPS > 1) {
             // ---------------- pass 1: stream sums
-            for (int b = b0; b < b1; b++) {
-                const int j0 = b * KB;
+            uint4 p0, p1;
+            if (nblk > 0) { load_perm(xperm, b0, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b0, p0, p1, rows, xval, C4, N, ln, WITH_K); }
+            else cp_async_commit();
+            if (nblk > 1) { load_perm(xperm, b0 + 1, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b0 + 1, p0, p1, rows, xval, C4, N, ln, WITH_K); }
+            else cp_async_commit();
+            if (nblk > 2) load_perm(xperm, b0 + 2, p0, p1);
+            for (int t = 0; t < nblk; t++) {
+                const int b = b0 + t, j0 = b * KB, cur = t % RING_DEPTH;
+                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b + 2, p0, p1, rows, xval, C4, N, ln, WITH_K);
+                else cp_async_commit();
+                if (t + 3 < nblk) load_perm(xperm, b + 3, p0, p1);
+                cp_async_wait<RING_DEPTH - 1>();
                 float kv[KB];
                 if (WITH_K) {
-                    float4 t0 = ldg4(xval + j0), t1 = ldg4(xval + j0 + 4);
-                    kv[0] = t0.x; kv[1] = t0.y; kv[2] = t0.z; kv[3] = t0.w;
-                    kv[4] = t1.x; kv[5] = t1.y; kv[6] = t1.z; kv[7] = t1.w;
+                    __syncwarp(gmask);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) kv[i] = sx[st][cur][i];
+                    __syncwarp(gmask);
                 }
-                uint32_t pr[KB];
-                {
-                    uint4 t0 = __ldg(reinterpret_cast<const uint4*>(xperm + j0));
-                    uint4 t1 = __ldg(reinterpret_cast<const uint4*>(xperm + j0 + 4));
-                    pr[0] = t0.x; pr[1] = t0.y; pr[2] = t0.z; pr[3] = t0.w;
-                    pr[4] = t1.x; pr[5] = t1.y; pr[6] = t1.z; pr[7] = t1.w;
-                }
-                PVec<CPL> v[KB];
-                #pragma unroll
-                for (int i = 0; i < KB; i++) pload_row<CPL>(v[i], rows + (long long)pr[i] * C4, on && (j0 + i < N));
+                Vec<CPL> v[KB];
+                ring_read<CPL>(ring, cur, j0, N, v);
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     #pragma unroll
@@ -103,7 +95,7 @@ __global__ void __launch_bounds__(PWALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk
                 if (WITH_K) sK[st][c0 + c] = PK.x[c];
             }
             __syncthreads();
-            for (int i = tid; i < SEGS * CW; i += PWALK_THREADS) {
+            for (int i = tid; i < SEGS * CW; i += WALK_THREADS) {
                 const int g = i / CW, c = i % CW;
                 float accv = 0.0f, acck = 0.0f;
                 for (int t = 0; t < SPS; t++) {
@@ -123,83 +115,107 @@ __global__ void __launch_bounds__(PWALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk
         }
 
         // emit-side constants
-        PVec<CPL> wt;
-        if (EMIT == EMIT_DOT) pload_row<CPL>(wt, a.wtotal + (long long)p * C4 + c0, on);
-        float*       out   = EMIT == EMIT_ROWS ? a.out + (long long)p * M * C4 + c0 : nullptr;
-        const float* g     = EMIT == EMIT_DOT ? a.g + (long long)p * M * C4 + c0 : nullptr;
-        float*       out_s = EMIT == EMIT_DOT ? a.out_s + (long long)(seg_on ? seg : 0) * M : nullptr;
+        Vec<CPL> wt;
+        wt.zero();
+        if (EMIT == EMIT_DOT) {
+            #pragma unroll
+            for (int c = 0; c < CPL; c += 4) {
+                const float4 t = ldg4(a.wtotal + (long long)p * C4 + c0l + c);
+                wt.x[c] = t.x; wt.x[c + 1] = t.y; wt.x[c + 2] = t.z; wt.x[c + 3] = t.w;
+            }
+        }
+        float*       out   = EMIT == EMIT_ROWS ? a.out + (long long)p * M * C4 + c0l : nullptr;
+        const float* g     = EMIT == EMIT_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
+        float*       out_s = EMIT == EMIT_DOT ? a.out_s + (long long)sg * M : nullptr;
 
         // ---------------- pass 2: forward with emission
-        for (int b = b0; b < b1; b++) {
-            const int j0 = b * KB;
-            float kv[KB];
-            if (WITH_K) {
-                float4 t0 = ldg4(xval + j0), t1 = ldg4(xval + j0 + 4);
-                kv[0] = t0.x; kv[1] = t0.y; kv[2] = t0.z; kv[3] = t0.w;
-                kv[4] = t1.x; kv[5] = t1.y; kv[6] = t1.z; kv[7] = t1.w;
-            }
-            uint32_t pr[KB];
-            {
-                uint4 t0 = __ldg(reinterpret_cast<const uint4*>(xperm + j0));
-                uint4 t1 = __ldg(reinterpret_cast<const uint4*>(xperm + j0 + 4));
-                pr[0] = t0.x; pr[1] = t0.y; pr[2] = t0.z; pr[3] = t0.w;
-                pr[4] = t1.x; pr[5] = t1.y; pr[6] = t1.z; pr[7] = t1.w;
-            }
-            uint32_t       m  = __ldg(mstart + b);
-            const uint32_t me = __ldg(mstart + b + 1);
-            PVec<CPL> v[KB], kb[WITH_K ? KB : 1];
-            #pragma unroll
-            for (int i = 0; i < KB; i++) pload_row<CPL>(v[i], rows + (long long)pr[i] * C4, on && (j0 + i < N));
-            // prefix states before each key, in place of the rows
-            #pragma unroll
-            for (int i = 0; i < KB; i++) {
-                #pragma unroll
-                for (int c = 0; c < CPL; c++) {
-                    float t = v[i].x[c];
-                    v[i].x[c] = PV.x[c];
-                    PV.x[c] += t;
-                    if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t, PK.x[c]); }
+        {
+            const uint4* yp  = a.yrec + (long long)sg * (M + 1) + (nblk > 0 ? __ldg(a.mstart + (long long)sg * mstride(N) + b0) : 0u);
+            uint4        rec = nblk > 0 ? __ldg(yp) : make_uint4(0, 0, 0, 0xffffffffu);
+            uint4 p0, p1;
+            if (nblk > 0) { load_perm(xperm, b0, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b0, p0, p1, rows, xval, C4, N, ln, WITH_K); }
+            else cp_async_commit();
+            if (nblk > 1) { load_perm(xperm, b0 + 1, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b0 + 1, p0, p1, rows, xval, C4, N, ln, WITH_K); }
+            else cp_async_commit();
+            if (nblk > 2) load_perm(xperm, b0 + 2, p0, p1);
+            for (int t = 0; t < nblk; t++) {
+                const int b = b0 + t, j0 = b * KB, cur = t % RING_DEPTH;
+                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b + 2, p0, p1, rows, xval, C4, N, ln, WITH_K);
+                else cp_async_commit();
+                if (t + 3 < nblk) load_perm(xperm, b + 3, p0, p1);
+                cp_async_wait<RING_DEPTH - 1>();
+                float kv[KB];
+                if (WITH_K) {
+                    __syncwarp(gmask);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) kv[i] = sx[st][cur][i];
+                    __syncwarp(gmask);
                 }
-            }
-            uint4 rec = m < me ? __ldg(yrec + m) : make_uint4(0, 0, 0, 0xffffffffu);
-            #pragma unroll
-            for (int i = 0; i < KB; i++) {
-                while (m < me && rec.w == (uint32_t)(j0 + i)) {
-                    const uint4 nxt = (m + 1 < me) ? __ldg(yrec + m + 1) : make_uint4(0, 0, 0, 0xffffffffu);
-                    if (EMIT == EMIT_ROWS) {
-                        const float e0 = __uint_as_float(rec.x);
-                        if (on) {
-                            float* o = out + (long long)rec.z * C4;
-                            #pragma unroll
-                            for (int c = 0; c < CPL; c += 4)
-                                red_add4(o + c,
-                                         fmaf(e0, v[i].x[c],     -2.0f * kb[WITH_K ? i : 0].x[c]),
-                                         fmaf(e0, v[i].x[c + 1], -2.0f * kb[WITH_K ? i : 0].x[c + 1]),
-                                         fmaf(e0, v[i].x[c + 2], -2.0f * kb[WITH_K ? i : 0].x[c + 2]),
-                                         fmaf(e0, v[i].x[c + 3], -2.0f * kb[WITH_K ? i : 0].x[c + 3]));
-                        }
-                    } else {
-                        PVec<CPL> gr;
-                        pload_row<CPL>(gr, g + (long long)rec.z * C4, on);
-                        float acc = 0.0f;
-                        #pragma unroll
-                        for (int c = 0; c < CPL; c++) acc = fmaf(gr.x[c], fmaf(2.0f, v[i].x[c], -wt.x[c]), acc);
-                        #pragma unroll
-                        for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
-                        if (seg_on && ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
+                Vec<CPL> v[KB], kb[WITH_K ? KB : 1];
+                ring_read<CPL>(ring, cur, j0, N, v);
+                // prefix states before each key, in place of the rows
+                #pragma unroll
+                for (int i = 0; i < KB; i++) {
+                    #pragma unroll
+                    for (int c = 0; c < CPL; c++) {
+                        const float t2 = v[i].x[c];
+                        v[i].x[c] = PV.x[c];
+                        PV.x[c] += t2;
+                        if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t2, PK.x[c]); }
                     }
-                    rec = nxt;
-                    m++;
+                }
+                #pragma unroll
+                for (int i = 0; i < KB; i++) {
+                    while (rec.w == (uint32_t)(j0 + i)) {
+                        const uint4 nxt = __ldg(++yp);
+                        if (EMIT == EMIT_ROWS) {
+                            const float e0 = __uint_as_float(rec.x);
+                            if (on) {
+                                float* o = out + (size_t)rec.z * C4;
+                                #pragma unroll
+                                for (int c = 0; c < CPL; c += 4)
+                                    red_add4(o + c,
+                                             fmaf(e0, v[i].x[c],     -2.0f * kb[WITH_K ? i : 0].x[c]),
+                                             fmaf(e0, v[i].x[c + 1], -2.0f * kb[WITH_K ? i : 0].x[c + 1]),
+                                             fmaf(e0, v[i].x[c + 2], -2.0f * kb[WITH_K ? i : 0].x[c + 2]),
+                                             fmaf(e0, v[i].x[c + 3], -2.0f * kb[WITH_K ? i : 0].x[c + 3]));
+                            }
+                        } else {
+                            float acc = 0.0f;
+                            if (lane_on) {
+                                const float* gr = g + (size_t)rec.z * C4;
+                                #pragma unroll
+                                for (int c = 0; c < CPL; c += 4) {
+                                    const float4 t4 = ldg4(gr + c);
+                                    acc = fmaf(t4.x, fmaf(2.0f, v[i].x[c],     -wt.x[c]),     acc);
+                                    acc = fmaf(t4.y, fmaf(2.0f, v[i].x[c + 1], -wt.x[c + 1]), acc);
+                                    acc = fmaf(t4.z, fmaf(2.0f, v[i].x[c + 2], -wt.x[c + 2]), acc);
+                                    acc = fmaf(t4.w, fmaf(2.0f, v[i].x[c + 3], -wt.x[c + 3]), acc);
+                                }
+                            }
+                            #pragma unroll
+                            for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
+                            if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
+                        }
+                        rec = nxt;
+                    }
                 }
             }
         }
-        if (SPS > 1) __syncthreads();
+        __syncthreads();
     }
 }
 
+template <int CPL>
+static size_t ring_bytes() { return (size_t)RING_DEPTH * KB * (CPL / 4) * WALK_THREADS * sizeof(float4); }
+
 template <int LPS, int CPL, int EMIT>
 static cudaError_t launch_pw(const WalkArgs& a, int grid, cudaStream_t stream) {
-    prefix_walk<LPS, CPL, EMIT><<<grid, PWALK_THREADS, 0, stream>>>(a);
+    auto kern = prefix_walk<LPS, CPL, EMIT>;
+    const size_t smem = ring_bytes<CPL>();
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    kern<<<grid, WALK_THREADS, smem, stream>>>(a);
     return cudaGetLastError();
 }
 

@@ -199,7 +199,7 @@ def sort_rank_records(x, y, mode):
         ws = torch.empty(int(n.value), dtype=torch.uint8, device=dev)
         xperm = torch.zeros(P * D, NP, dtype=torch.int32, device=dev)
         xval = torch.zeros(P * D, NP + 8, dtype=torch.float32, device=dev)
-        yrec = torch.zeros(P * D, M, 4, dtype=torch.int32, device=dev)
+        yrec = torch.zeros(P * D, M + 1, 4, dtype=torch.int32, device=dev)
         mstart = torch.zeros(P * D, MS, dtype=torch.int32, device=dev)
         st = L.qlka_sort_rank_records(x.data_ptr(), y.data_ptr(), xperm.data_ptr(), xval.data_ptr(), yrec.data_ptr(),
                                       mstart.data_ptr(), ws.data_ptr(), int(n.value), P, D, N, M, int(mode), _stream())

@@ -47,7 +47,8 @@ def test_records(shape, mode):
             want = np.zeros(NP + 8, np.float32)
             want[:N] = sx
             assert np.array_equal(xval[s], want)
-        rec = yrec[s]
+        assert yrec[s, M, 3] == -1, "sentinel record"
+        rec = yrec[s, :M]
         rows = rec[:, 2].astype(np.int64)
         assert sorted(rows.tolist()) == list(range(M)), "query rows are not a permutation"
         sy = ys[rows]

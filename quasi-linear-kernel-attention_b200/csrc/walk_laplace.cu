@@ -7,7 +7,8 @@
 //   * LPS lanes cooperate on one "stream" (a contiguous run of key blocks of one segment),
 //     each lane owning CPL consecutive channels, so a row is one or two 16-byte copies per
 //     lane and a result is one or two 16-byte vector reductions; lanes never exchange rows.
-//   * rows reach the lanes through the cp.async ring of walk_ring.cuh, two blocks ahead.
+//   * rows, per-key decays and query records reach the lanes through the cp.async staging of
+//     walk_ring.cuh, two blocks ahead of their use.
 //   * pass 1 walks the stream backwards once: the local suffix state at every block start
 //     goes to a per-CTA checkpoint buffer (L2 resident), the stream's forward and backward
 //     aggregates to shared memory.
@@ -15,8 +16,7 @@
 //     incoming prefix state and incoming suffix state.
 //   * pass 2 walks forward: per block of 8 keys the suffix states are rebuilt in registers
 //     from the next checkpoint, the prefix states overwrite the row registers, and the
-//     queries of the block are emitted in rank order from a running cursor into the query
-//     records (which end in a sentinel, so the cursor needs no bound).
+//     block's queries are emitted in rank order.
 // The rows are therefore gathered twice (the reference gathers them three times) and every
 // exponential was already taken by the sort/rank kernel.
 #include "walk_ring.cuh"
@@ -28,10 +28,13 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
 {
     constexpr int STREAMS = WALK_THREADS / LPS;
     constexpr int CW      = LPS * CPL;               // channel capacity of a stream
-    extern __shared__ __align__(16) float4 ring[];   // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
-    __shared__ __align__(16) float sx[STREAMS][RING_DEPTH][SX_STRIDE];
-    __shared__ float sF[STREAMS][CW];                // forward aggregate  -> incoming prefix state
-    __shared__ float sB[STREAMS][CW];                // backward aggregate -> incoming suffix state
+    extern __shared__ __align__(16) float4 smem[];
+    float4* ring  = smem;                                                    // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
+    uint4*  qs_all = reinterpret_cast<uint4*>(ring + RING_DEPTH * ring_slot_f4<CPL>());   // [STREAMS][RING_DEPTH][LPS]
+    float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);       // [STREAMS][RING_DEPTH][SX_STRIDE]
+    // stream aggregates live in the ring's memory between the two passes
+    float (*sF)[CW] = reinterpret_cast<float (*)[CW]>(ring);                 // forward aggregate  -> incoming prefix state
+    float (*sB)[CW] = sF + STREAMS;                                          // backward aggregate -> incoming suffix state
     __shared__ float sAF[STREAMS], sAB[STREAMS];     // total decay across the stream (forward / backward)
 
     const int tid = threadIdx.x;
@@ -46,6 +49,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
     const int  c0l     = lane_on ? c0 : 0;           // idle lanes shadow lane 0's loads and store nothing
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
 
+    Feeder<LPS, CPL> f;
+    f.ring = ring + tid;
+    f.qs   = qs_all + st * RING_DEPTH * LPS;
+    f.sxs  = sx_all + st * RING_DEPTH * SX_STRIDE;
+    f.C4 = C4; f.N = N; f.ln = ln; f.gmask = gmask; f.with_x = true;
+
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
         const bool seg_on = seg < a.nseg;
@@ -56,39 +65,40 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
         const int  b1     = seg_on ? (int)((long long)(s + 1) * NBK / SPS) : 0;
         const int  nblk   = b1 - b0;
 
-        const uint32_t* xperm = a.xperm + (long long)sg * NP;
-        const float*    xval  = a.xval + (long long)sg * xstride(N);
-        const float*    rows  = a.rows + (long long)p * N * C4 + c0l;
-        float*          out   = a.out + (long long)p * M * C4 + c0l;
-        const long long slot  = (long long)blockIdx.x * SEGS + sl;
-        float*          ck    = a.ckpt + slot * NBK * C4 + c0l;
-        float*          wk    = a.wck + slot * NBK;
+        f.xperm  = a.xperm + (long long)sg * NP;
+        f.xval   = a.xval + (long long)sg * xstride(N);
+        f.rows   = a.rows + (long long)p * N * C4 + c0l;
+        f.mstart = a.mstart + (long long)sg * mstride(N);
+        f.yrec   = a.yrec + (long long)sg * (M + 1);
+        float*          out  = a.out + (long long)p * M * C4 + c0l;
+        const long long slot = (long long)blockIdx.x * SEGS + sl;
+        float*          ck   = a.ckpt + slot * NBK * C4 + c0l;
+        float*          wk   = a.wck + slot * NBK;
 
         // ---------------- pass 1: backward over the stream
         Vec<CPL> Rl, F;
         Rl.zero(); F.zero();
         float w = 1.0f, wprev = 1.0f;
-        const float a_j1 = (seg_on && b1 < NBK) ? __ldg(xval + b1 * KB) : 0.0f;   // decay from the next stream's first key
+        const float a_j1 = (seg_on && b1 < NBK) ? __ldg(f.xval + b1 * KB) : 0.0f;   // decay from the next stream's first key
         {
-            uint4 p0, p1;
-            if (nblk > 0) { load_perm(xperm, b1 - 1, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b1 - 1, p0, p1, rows, xval, C4, N, ln, true); }
-            else cp_async_commit();
-            if (nblk > 1) { load_perm(xperm, b1 - 2, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b1 - 2, p0, p1, rows, xval, C4, N, ln, true); }
-            else cp_async_commit();
-            if (nblk > 2) load_perm(xperm, b1 - 3, p0, p1);
+            f.with_q = false;
+            if (nblk > 0) { f.prefetch_index(b1 - 1); f.issue(0, b1 - 1); } else cp_async_commit();
+            if (nblk > 1) { f.prefetch_index(b1 - 2); f.issue(1, b1 - 2); } else cp_async_commit();
+            if (nblk > 2) f.prefetch_index(b1 - 3);
+            int cur = 0;
             for (int t = 0; t < nblk; t++) {
-                const int b = b1 - 1 - t, j0 = b * KB, cur = t % RING_DEPTH;
-                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b - 2, p0, p1, rows, xval, C4, N, ln, true);
-                else cp_async_commit();
-                if (t + 3 < nblk) load_perm(xperm, b - 3, p0, p1);
+                const int b = b1 - 1 - t, j0 = b * KB;
+                __syncwarp(gmask);                     // every lane is done with the slot refilled below
+                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b - 2); else cp_async_commit();
+                if (t + 3 < nblk) f.prefetch_index(b - 3);
                 cp_async_wait<RING_DEPTH - 1>();
                 __syncwarp(gmask);
                 float av[KB + 1];
+                const float* sx = f.sxs + cur * SX_STRIDE;
                 #pragma unroll
-                for (int i = 0; i <= KB; i++) av[i] = sx[st][cur][i];
-                __syncwarp(gmask);
+                for (int i = 0; i <= KB; i++) av[i] = sx[i];
                 Vec<CPL> v[KB];
-                ring_read<CPL>(ring, cur, j0, N, v);
+                f.read_rows(cur, j0, v);
                 #pragma unroll
                 for (int i = KB - 1; i >= 0; i--) {
                     #pragma unroll
@@ -105,8 +115,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                         *reinterpret_cast<float4*>(ck + (long long)b * C4 + c) = make_float4(Rl.x[c], Rl.x[c + 1], Rl.x[c + 2], Rl.x[c + 3]);
                 }
                 if (seg_on && ln == 0) wk[b] = wprev * a_j1;
+                cur = ring_next(cur);
             }
         }
+        __syncthreads();        // every thread has left the ring: its memory now holds the aggregates
         #pragma unroll
         for (int c = 0; c < CPL; c++) { sF[st][c0 + c] = F.x[c]; sB[st][c0 + c] = Rl.x[c]; }
         if (ln == 0) { sAF[st] = w; sAB[st] = wprev * a_j1; }
@@ -118,9 +130,9 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
             float L = 0.0f;
             for (int t = 0; t < SPS; t++) {
                 const int q = g * SPS + t;
-                float f = sF[q][c];
+                float fv = sF[q][c];
                 sF[q][c] = L;
-                L = fmaf(sAF[q], L, f);
+                L = fmaf(sAF[q], L, fv);
             }
             float R = 0.0f;
             for (int t = SPS - 1; t >= 0; t--) {
@@ -131,23 +143,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
             }
         }
         __syncthreads();
-
-        // ---------------- pass 2: forward with emission
         Vec<CPL> L, Rin;
         #pragma unroll
         for (int c = 0; c < CPL; c++) { L.x[c] = sF[st][c0 + c]; Rin.x[c] = sB[st][c0 + c]; }
-        {
-            // query cursor: records of this stream start at mstart[b0]; the next stream's first record
-            // (or the sentinel after the last query) has a rank beyond this stream's positions
-            const uint4* yp  = a.yrec + (long long)sg * (M + 1) + (nblk > 0 ? __ldg(a.mstart + (long long)sg * mstride(N) + b0) : 0u);
-            uint4        rec = nblk > 0 ? __ldg(yp) : make_uint4(0, 0, 0, 0xffffffffu);
+        __syncthreads();        // aggregates are in registers: the ring may be refilled
 
-            uint4 p0, p1;
-            if (nblk > 0) { load_perm(xperm, b0, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b0, p0, p1, rows, xval, C4, N, ln, true); }
-            else cp_async_commit();
-            if (nblk > 1) { load_perm(xperm, b0 + 1, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b0 + 1, p0, p1, rows, xval, C4, N, ln, true); }
-            else cp_async_commit();
-            if (nblk > 2) load_perm(xperm, b0 + 2, p0, p1);
+        // ---------------- pass 2: forward with emission
+        {
+            f.with_q = true;
+            if (nblk > 0) { f.prefetch_index(b0); f.issue(0, b0); } else cp_async_commit();
+            if (nblk > 1) { f.prefetch_index(b0 + 1); f.issue(1, b0 + 1); } else cp_async_commit();
+            if (nblk > 2) f.prefetch_index(b0 + 2);
             // checkpoint of the block after the current one, fetched one iteration early
             Vec<CPL> cnext; cnext.zero();
             float    wnext = 0.0f;
@@ -163,11 +169,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
             };
             load_ckpt(b0 + 1);
 
+            int cur = 0;
             for (int t = 0; t < nblk; t++) {
-                const int b = b0 + t, j0 = b * KB, cur = t % RING_DEPTH;
-                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b + 2, p0, p1, rows, xval, C4, N, ln, true);
-                else cp_async_commit();
-                if (t + 3 < nblk) load_perm(xperm, b + 3, p0, p1);
+                const int b = b0 + t, j0 = b * KB;
+                __syncwarp(gmask);
+                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
+                if (t + 3 < nblk) f.prefetch_index(b + 3);
 
                 // suffix state entering the block from above: corrected checkpoint, or the stream's incoming state
                 Vec<CPL> Rn;
@@ -182,11 +189,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                 cp_async_wait<RING_DEPTH - 1>();
                 __syncwarp(gmask);
                 float av[KB + 1];
+                const float* sx = f.sxs + cur * SX_STRIDE;
                 #pragma unroll
-                for (int i = 0; i <= KB; i++) av[i] = sx[st][cur][i];
-                __syncwarp(gmask);
+                for (int i = 0; i <= KB; i++) av[i] = sx[i];
+                const uint32_t m_lo = __float_as_uint(sx[9]), cnt = __float_as_uint(sx[10]) - m_lo;
                 Vec<CPL> v[KB];
-                ring_read<CPL>(ring, cur, j0, N, v);
+                f.read_rows(cur, j0, v);
 
                 Vec<CPL> Rb[KB];
                 #pragma unroll
@@ -204,11 +212,18 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                         L.x[c] = fmaf(av[i], L.x[c], t2);
                     }
                 }
-                // the block's queries, in rank order
+                // the block's queries, in rank order: the first LPS from the staged slot, any others from memory
+                const uint4* qslot = f.qs + cur * LPS;
+                auto fetch = [&](uint32_t n) -> uint4 {
+                    if (n >= cnt) return make_uint4(0u, 0u, 0u, 0xffffffffu);
+                    return n < (uint32_t)LPS ? qslot[n] : __ldg(f.yrec + m_lo + n);
+                };
+                uint32_t n   = 0;
+                uint4    rec = fetch(0);
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     while (rec.w == (uint32_t)(j0 + i)) {
-                        const uint4 nxt = __ldg(++yp);
+                        const uint4 nxt = fetch(++n);
                         const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
                         if (on) {
                             float* o = out + (size_t)rec.z * C4;
@@ -223,19 +238,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                         rec = nxt;
                     }
                 }
+                cur = ring_next(cur);
             }
         }
-        __syncthreads();        // shared aggregates and the ring are rewritten by the next item
+        __syncthreads();        // the ring and the aggregates are rewritten by the next item
     }
 }
-
-template <int CPL>
-static size_t ring_bytes() { return (size_t)RING_DEPTH * KB * (CPL / 4) * WALK_THREADS * sizeof(float4); }
 
 template <int LPS, int CPL>
 static cudaError_t launch_lap(const WalkArgs& a, int grid, cudaStream_t stream) {
     auto kern = laplace_walk<LPS, CPL>;
-    const size_t smem = ring_bytes<CPL>();
+    const size_t smem = walk_smem_bytes<LPS, CPL>();
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<grid, WALK_THREADS, smem, stream>>>(a);

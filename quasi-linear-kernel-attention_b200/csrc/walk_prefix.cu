@@ -9,10 +9,10 @@
 //              (Weighted_Abs_Sum/csrc/sgn_kernels.cu:8-15, sgn_prefix :17-192); one writer per
 //              output element, plain stores.
 //
-// Same thread mapping and row staging as the Laplace walk (LPS lanes per stream, CPL channels
-// per lane, SPS streams per segment, persistent CTAs, cp.async ring). Pass 1 sums each
-// stream's rows, a shared-memory scan turns the sums into each stream's incoming prefix,
-// pass 2 walks forward and emits. With one stream per segment pass 1 and the scan are skipped.
+// Same thread mapping and staging as the Laplace walk (LPS lanes per stream, CPL channels per
+// lane, SPS streams per segment, persistent CTAs, cp.async ring). Pass 1 sums each stream's
+// rows, a shared-memory scan turns the sums into each stream's incoming prefix, pass 2 walks
+// forward and emits. With one stream per segment pass 1 and the scan are skipped.
 #include "walk_ring.cuh"
 
 namespace qlka {
@@ -25,10 +25,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
     constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr int  CW      = LPS * CPL;
     constexpr bool WITH_K  = EMIT == EMIT_ROWS;
-    extern __shared__ __align__(16) float4 ring[];
-    __shared__ __align__(16) float sx[STREAMS][RING_DEPTH][SX_STRIDE];
-    __shared__ float sV[STREAMS][CW];
-    __shared__ float sK[WITH_K ? STREAMS : 1][WITH_K ? CW : 1];
+    extern __shared__ __align__(16) float4 smem[];
+    float4* ring   = smem;
+    uint4*  qs_all = reinterpret_cast<uint4*>(ring + RING_DEPTH * ring_slot_f4<CPL>());
+    float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);
+    float (*sV)[CW] = reinterpret_cast<float (*)[CW]>(ring);     // stream sums, in the ring's memory between the passes
+    float (*sK)[CW] = sV + STREAMS;
 
     const int tid = threadIdx.x;
     const int st  = tid / LPS, ln = tid % LPS, c0 = ln * CPL;
@@ -40,6 +42,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
     const int  c0l     = lane_on ? c0 : 0;
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
 
+    Feeder<LPS, CPL> f;
+    f.ring = ring + tid;
+    f.qs   = qs_all + st * RING_DEPTH * LPS;
+    f.sxs  = sx_all + st * RING_DEPTH * SX_STRIDE;
+    f.C4 = C4; f.N = N; f.ln = ln; f.gmask = gmask; f.with_x = WITH_K;
+
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
         const bool seg_on = seg < a.nseg;
@@ -50,36 +58,37 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
         const int  b1     = seg_on ? (int)((long long)(s + 1) * NBK / SPS) : 0;
         const int  nblk   = b1 - b0;
 
-        const uint32_t* xperm = a.xperm + (long long)sg * NP;
-        const float*    xval  = WITH_K ? a.xval + (long long)sg * xstride(N) : nullptr;
-        const float*    rows  = a.rows + (long long)p * N * C4 + c0l;
+        f.xperm  = a.xperm + (long long)sg * NP;
+        f.xval   = WITH_K ? a.xval + (long long)sg * xstride(N) : nullptr;
+        f.rows   = a.rows + (long long)p * N * C4 + c0l;
+        f.mstart = a.mstart + (long long)sg * mstride(N);
+        f.yrec   = a.yrec + (long long)sg * (M + 1);
 
         Vec<CPL> PV, PK;
         PV.zero(); PK.zero();
 
         if (SPS > 1) {
             // ---------------- pass 1: stream sums
-            uint4 p0, p1;
-            if (nblk > 0) { load_perm(xperm, b0, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b0, p0, p1, rows, xval, C4, N, ln, WITH_K); }
-            else cp_async_commit();
-            if (nblk > 1) { load_perm(xperm, b0 + 1, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b0 + 1, p0, p1, rows, xval, C4, N, ln, WITH_K); }
-            else cp_async_commit();
-            if (nblk > 2) load_perm(xperm, b0 + 2, p0, p1);
+            f.with_q = false;
+            if (nblk > 0) { f.prefetch_index(b0); f.issue(0, b0); } else cp_async_commit();
+            if (nblk > 1) { f.prefetch_index(b0 + 1); f.issue(1, b0 + 1); } else cp_async_commit();
+            if (nblk > 2) f.prefetch_index(b0 + 2);
+            int cur = 0;
             for (int t = 0; t < nblk; t++) {
-                const int b = b0 + t, j0 = b * KB, cur = t % RING_DEPTH;
-                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b + 2, p0, p1, rows, xval, C4, N, ln, WITH_K);
-                else cp_async_commit();
-                if (t + 3 < nblk) load_perm(xperm, b + 3, p0, p1);
+                const int b = b0 + t, j0 = b * KB;
+                __syncwarp(gmask);
+                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
+                if (t + 3 < nblk) f.prefetch_index(b + 3);
                 cp_async_wait<RING_DEPTH - 1>();
                 float kv[KB];
                 if (WITH_K) {
                     __syncwarp(gmask);
+                    const float* sx = f.sxs + cur * SX_STRIDE;
                     #pragma unroll
-                    for (int i = 0; i < KB; i++) kv[i] = sx[st][cur][i];
-                    __syncwarp(gmask);
+                    for (int i = 0; i < KB; i++) kv[i] = sx[i];
                 }
                 Vec<CPL> v[KB];
-                ring_read<CPL>(ring, cur, j0, N, v);
+                f.read_rows(cur, j0, v);
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     #pragma unroll
@@ -88,7 +97,9 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         if (WITH_K) PK.x[c] = fmaf(kv[i], v[i].x[c], PK.x[c]);
                     }
                 }
+                cur = ring_next(cur);
             }
+            __syncthreads();        // every thread has left the ring: its memory now holds the sums
             #pragma unroll
             for (int c = 0; c < CPL; c++) {
                 sV[st][c0 + c] = PV.x[c];
@@ -112,6 +123,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                 PV.x[c] = sV[st][c0 + c];
                 if (WITH_K) PK.x[c] = sK[st][c0 + c];
             }
+            __syncthreads();        // prefixes are in registers: the ring may be refilled
         }
 
         // emit-side constants
@@ -130,29 +142,27 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
 
         // ---------------- pass 2: forward with emission
         {
-            const uint4* yp  = a.yrec + (long long)sg * (M + 1) + (nblk > 0 ? __ldg(a.mstart + (long long)sg * mstride(N) + b0) : 0u);
-            uint4        rec = nblk > 0 ? __ldg(yp) : make_uint4(0, 0, 0, 0xffffffffu);
-            uint4 p0, p1;
-            if (nblk > 0) { load_perm(xperm, b0, p0, p1); ring_issue<CPL>(ring, sx[st][0], 0, b0, p0, p1, rows, xval, C4, N, ln, WITH_K); }
-            else cp_async_commit();
-            if (nblk > 1) { load_perm(xperm, b0 + 1, p0, p1); ring_issue<CPL>(ring, sx[st][1], 1, b0 + 1, p0, p1, rows, xval, C4, N, ln, WITH_K); }
-            else cp_async_commit();
-            if (nblk > 2) load_perm(xperm, b0 + 2, p0, p1);
+            f.with_q = true;
+            if (nblk > 0) { f.prefetch_index(b0); f.issue(0, b0); } else cp_async_commit();
+            if (nblk > 1) { f.prefetch_index(b0 + 1); f.issue(1, b0 + 1); } else cp_async_commit();
+            if (nblk > 2) f.prefetch_index(b0 + 2);
+            int cur = 0;
             for (int t = 0; t < nblk; t++) {
-                const int b = b0 + t, j0 = b * KB, cur = t % RING_DEPTH;
-                if (t + 2 < nblk) ring_issue<CPL>(ring, sx[st][(t + 2) % RING_DEPTH], (t + 2) % RING_DEPTH, b + 2, p0, p1, rows, xval, C4, N, ln, WITH_K);
-                else cp_async_commit();
-                if (t + 3 < nblk) load_perm(xperm, b + 3, p0, p1);
+                const int b = b0 + t, j0 = b * KB;
+                __syncwarp(gmask);
+                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
+                if (t + 3 < nblk) f.prefetch_index(b + 3);
                 cp_async_wait<RING_DEPTH - 1>();
+                __syncwarp(gmask);
+                const float* sx = f.sxs + cur * SX_STRIDE;
                 float kv[KB];
                 if (WITH_K) {
-                    __syncwarp(gmask);
                     #pragma unroll
-                    for (int i = 0; i < KB; i++) kv[i] = sx[st][cur][i];
-                    __syncwarp(gmask);
+                    for (int i = 0; i < KB; i++) kv[i] = sx[i];
                 }
+                const uint32_t m_lo = __float_as_uint(sx[9]), cnt = __float_as_uint(sx[10]) - m_lo;
                 Vec<CPL> v[KB], kb[WITH_K ? KB : 1];
-                ring_read<CPL>(ring, cur, j0, N, v);
+                f.read_rows(cur, j0, v);
                 // prefix states before each key, in place of the rows
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
@@ -164,10 +174,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t2, PK.x[c]); }
                     }
                 }
+                const uint4* qslot = f.qs + cur * LPS;
+                auto fetch = [&](uint32_t n) -> uint4 {
+                    if (n >= cnt) return make_uint4(0u, 0u, 0u, 0xffffffffu);
+                    return n < (uint32_t)LPS ? qslot[n] : __ldg(f.yrec + m_lo + n);
+                };
+                uint32_t n   = 0;
+                uint4    rec = fetch(0);
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     while (rec.w == (uint32_t)(j0 + i)) {
-                        const uint4 nxt = __ldg(++yp);
+                        const uint4 nxt = fetch(++n);
                         if (EMIT == EMIT_ROWS) {
                             const float e0 = __uint_as_float(rec.x);
                             if (on) {
@@ -200,19 +217,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         rec = nxt;
                     }
                 }
+                cur = ring_next(cur);
             }
         }
         __syncthreads();
     }
 }
 
-template <int CPL>
-static size_t ring_bytes() { return (size_t)RING_DEPTH * KB * (CPL / 4) * WALK_THREADS * sizeof(float4); }
-
 template <int LPS, int CPL, int EMIT>
 static cudaError_t launch_pw(const WalkArgs& a, int grid, cudaStream_t stream) {
     auto kern = prefix_walk<LPS, CPL, EMIT>;
-    const size_t smem = ring_bytes<CPL>();
+    const size_t smem = walk_smem_bytes<LPS, CPL>();
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<grid, WALK_THREADS, smem, stream>>>(a);

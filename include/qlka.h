@@ -37,7 +37,8 @@ enum qlka_status {
     QLKA_ERR_NULL = 7,             /* a required pointer is NULL */
     QLKA_ERR_WORKSPACE = 8,        /* workspace too small or misaligned (256 bytes) */
     QLKA_ERR_CUDA = 9,             /* a CUDA runtime call failed; see qlka_last_cuda_error */
-    QLKA_ERR_UNSUPPORTED = 10      /* a size inside the limits that this build has no kernel for */
+    QLKA_ERR_UNSUPPORTED = 10,     /* a size inside the limits that this build has no kernel for */
+    QLKA_ERR_NO_ALLOC_LIMIT = 11   /* problem too large for the fixed scratch of the *_noalloc entry point */
 };
 
 /* Human-readable text of a status code (static storage). */
@@ -55,6 +56,24 @@ int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const floa
                                       float* out_w, float* out_u,
                                       void* workspace, size_t workspace_bytes,
                                       int P, int D, int N, int M, int C, qlka_stream_t stream);
+
+/* The same operator for callers that cannot hand over a workspace and must not trigger an
+ * allocation: code running between cudaStreamBeginCapture and EndCapture, latency-critical
+ * serving loops (cudaMalloc serialises the whole device), and hosts whose own memory pool already
+ * owns all of HBM. The scratch is a fixed array of qlka_noalloc_scratch_bytes() (32 MiB) inside
+ * the library image; every GPU that loads the library keeps that much reserved until the process
+ * exits. Problems whose scratch would not fit are refused with QLKA_ERR_NO_ALLOC_LIMIT (roughly:
+ * P*D*(N+M) above a few hundred thousand elements) - use the workspace variant for those. The call
+ * allocates nothing and frees nothing. The first call on each device looks up the array's device
+ * address (one cheap runtime query); make that call once outside any stream capture. All calls
+ * share the one array: two calls whose kernels can overlap on the GPU (different streams, or
+ * different host threads) corrupt each other, so serialise them. Nothing needs to be cleared
+ * between calls. This entry point has no counterpart in the reference, whose operators allocate
+ * through the torch caching allocator. */
+size_t qlka_noalloc_scratch_bytes(void);
+int qlka_weighted_laplace_sum_forward_noalloc(const float* q, const float* k, const float* v,
+                                              float* out_w, float* out_u,
+                                              int P, int D, int N, int M, int C, qlka_stream_t stream);
 
 /* Diagnostic: the same call, but it waits for completion and reports the device time of the
  * sort/rank kernel and of the walk kernel (CUDA events on `stream`), in milliseconds.

@@ -201,6 +201,7 @@ const char* qlka_status_string(int status) {
         case QLKA_ERR_WORKSPACE:         return "workspace too small or not 256-byte aligned";
         case QLKA_ERR_CUDA:              return "a CUDA runtime call failed";
         case QLKA_ERR_UNSUPPORTED:       return "no kernel in this build for max(N,M) > 16384";
+        case QLKA_ERR_NO_ALLOC_LIMIT:    return "problem needs more scratch than the fixed 32 MiB of the no-allocation entry point; use the workspace variant";
         default:                         return "unknown status";
     }
 }
@@ -277,6 +278,47 @@ int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v
     }
     for (int i = 0; i < 3; i++) cudaEventDestroy(ev[i]);
     return st;
+}
+
+// ---------------------------------------------------------------- Laplace, fixed scratch
+// Scratch for qlka_weighted_laplace_sum_forward_noalloc: lives in the library image, so every
+// device that loads the library reserves QLKA_NOALLOC_SCRATCH_BYTES for as long as the process runs.
+constexpr size_t QLKA_NOALLOC_SCRATCH_BYTES = size_t(32) << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[QLKA_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not an address a kernel could
+// use: the device address is looked up once per device (with that device current) and cached.
+static int noalloc_scratch(void** out) {
+    constexpr int MAX_DEV = 64;
+    static void* cached[MAX_DEV] = {};
+    int dev = 0;
+    CU(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MAX_DEV) return QLKA_ERR_UNSUPPORTED;
+    if (!cached[dev]) {
+        void* ptr = nullptr;
+        CU(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        cached[dev] = ptr;      // racing first calls store the same value
+    }
+    *out = cached[dev];
+    return QLKA_OK;
+}
+
+size_t qlka_noalloc_scratch_bytes(void) { return QLKA_NOALLOC_SCRATCH_BYTES; }
+
+int qlka_weighted_laplace_sum_forward_noalloc(const float* q, const float* k, const float* v,
+                                              float* out_w, float* out_u,
+                                              int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (LaplaceWs(nullptr, P, D, N, M, C).bytes > QLKA_NOALLOC_SCRATCH_BYTES) return QLKA_ERR_NO_ALLOC_LIMIT;
+    void* scratch = nullptr;
+    st = noalloc_scratch(&scratch);
+    if (st) return st;
+    // every byte of scratch that the kernels read is written earlier in the same call, and the
+    // outputs are zeroed by the call itself, so what a previous call left behind is never seen
+    return laplace_forward_impl(q, k, v, out_w, out_u, scratch, QLKA_NOALLOC_SCRATCH_BYTES, P, D, N, M, C,
+                                reinterpret_cast<cudaStream_t>(stream_), nullptr);
 }
 
 // ---------------------------------------------------------------- abs forward

@@ -40,6 +40,9 @@ def lib():
         L.qlka_weighted_laplace_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_laplace_forward_stage_ms.restype = _i
         L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 2
+        L.qlka_noalloc_scratch_bytes.restype = _sz
+        L.qlka_weighted_laplace_sum_forward_noalloc.restype = _i
+        L.qlka_weighted_laplace_sum_forward_noalloc.argtypes = [_vp] * 5 + [_i] * 5 + [_vp]
         L.qlka_weighted_abs_sum_forward.restype = _i
         L.qlka_weighted_abs_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 6 + [_vp]
         L.qlka_weighted_abs_sum_backward.restype = _i
@@ -105,6 +108,27 @@ def laplace_forward(q, k, v):
         out_u = torch.empty(P, M, dtype=torch.float32, device=q.device)
         st = L.qlka_weighted_laplace_sum_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(), out_u.data_ptr(),
                                                  ws.data_ptr(), n, P, D, N, M, C, _stream())
+    if st:
+        _raise(st)
+    return out_w, out_u
+
+
+def laplace_forward_noalloc(q, k, v, out_w=None, out_u=None):
+    """weighted Laplace sum through the entry point that uses the library's fixed scratch array
+    instead of a workspace. The native call allocates nothing; pass preallocated `out_w` (P, M, C)
+    and `out_u` (P, M) to keep this wrapper from allocating too. Raises if the problem needs more
+    scratch than the array holds. Calls must not overlap on the GPU (they share the array)."""
+    P, D, N, M, C = check_qkv(q, k, v)
+    L = lib()
+    with torch.cuda.device(q.device):
+        if out_w is None:
+            out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
+        if out_u is None:
+            out_u = torch.empty(P, M, dtype=torch.float32, device=q.device)
+        _check_like(out_w, "out_w", (P, M, C), q)
+        _check_like(out_u, "out_u", (P, M), q)
+        st = L.qlka_weighted_laplace_sum_forward_noalloc(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(),
+                                                         out_u.data_ptr(), P, D, N, M, C, _stream())
     if st:
         _raise(st)
     return out_w, out_u

@@ -104,35 +104,70 @@ __device__ __forceinline__ void load_segment(const float* __restrict__ src, cons
     }
 }
 
-// ------------------------------------------------------------------ block scan of x_j = A_j x_{j-1} + B_j
-// Inclusive, x_{-1} = 0, j = 0..n-1 in scan order; `elem(i, A, B)` gives the coefficients of
-// scan position i and `store(i, x)` receives the result. Each thread owns a contiguous run.
-template <int THREADS, class Elem, class Store>
-__device__ __forceinline__ void block_affine_scan(const int n, float* __restrict__ wa, float* __restrict__ wb,
-                                                  Elem elem, Store store)
+// ------------------------------------------------------------------ block scans
+// x_j = A_j x_{j-1} + B_j, inclusive, x_{-1} = 0, over scan positions 0..n-1. Every thread owns
+// the contiguous run [i0, i1) and passes the coefficients of its run in registers
+// (for position i0 + k); on return the B array holds x at position i0 + k.
+template <int THREADS, int E, bool REV, int OFF>
+__device__ __forceinline__ void block_affine_scan(const int cnt, const float (&AA)[E + 1], float (&BX)[E],
+                                                  float* __restrict__ wa, float* __restrict__ wb)
 {
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int per = (n + THREADS - 1) / THREADS;
-    const int i0  = min(n, tid * per), i1 = min(n, i0 + per);
-
+    // coefficient of run element k: A = AA[k + OFF]; BX holds B on entry and x on return
+    // REV = false: positions ascend with k, thread and lane index. REV = true: the scan runs from the
+    // last position to the first (k, lane and warp all descending); empty runs act as the identity.
+    constexpr int W = THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float a = 1.0f, b = 0.0f;                     // composite of my run: x -> a x + b
-    for (int i = i0; i < i1; i++) { float A, B; elem(i, A, B); a = A * a; b = A * b + B; }
-
-    float ia = a, ib = b;                         // inclusive over lanes
+    #pragma unroll
+    for (int kk = 0; kk < E; kk++) {
+        const int k = REV ? E - 1 - kk : kk;
+        if (k < cnt) { a = AA[k + OFF] * a; b = fmaf(AA[k + OFF], b, BX[k]); }
+    }
+    float ia = a, ib = b;                         // inclusive over lanes, in scan order
     #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-        float pa = __shfl_up_sync(FULL, ia, off), pb = __shfl_up_sync(FULL, ib, off);
-        if (lane >= off) { ib = ia * pb + ib; ia = ia * pa; }
+        float pa = REV ? __shfl_down_sync(FULL, ia, off) : __shfl_up_sync(FULL, ia, off);
+        float pb = REV ? __shfl_down_sync(FULL, ib, off) : __shfl_up_sync(FULL, ib, off);
+        if (REV ? (lane + off < 32) : (lane >= off)) { ib = fmaf(ia, pb, ib); ia = ia * pa; }
     }
     __syncthreads();                              // wa/wb may still be read by a previous scan
-    if (lane == 31) { wa[warp] = ia; wb[warp] = ib; }
+    if (lane == (REV ? 0 : 31)) { wa[warp] = ia; wb[warp] = ib; }
     __syncthreads();
     float pb = 0.0f;                              // state entering my warp
-    for (int w = 0; w < warp; w++) pb = wa[w] * pb + wb[w];
-    float ea = __shfl_up_sync(FULL, ia, 1), eb = __shfl_up_sync(FULL, ib, 1);
-    if (lane == 0) { ea = 1.0f; eb = 0.0f; }
-    float x = ea * pb + eb;                       // state entering my run
-    for (int i = i0; i < i1; i++) { float A, B; elem(i, A, B); x = A * x + B; store(i, x); }
+    if (REV) { for (int w = W - 1; w > warp; w--) pb = fmaf(wa[w], pb, wb[w]); }
+    else     { for (int w = 0; w < warp; w++)     pb = fmaf(wa[w], pb, wb[w]); }
+    float ea = REV ? __shfl_down_sync(FULL, ia, 1) : __shfl_up_sync(FULL, ia, 1);
+    float eb = REV ? __shfl_down_sync(FULL, ib, 1) : __shfl_up_sync(FULL, ib, 1);
+    if (lane == (REV ? 31 : 0)) { ea = 1.0f; eb = 0.0f; }
+    float x = fmaf(ea, pb, eb);                   // state entering my run
+    #pragma unroll
+    for (int kk = 0; kk < E; kk++) {
+        const int k = REV ? E - 1 - kk : kk;
+        if (k < cnt) { x = fmaf(AA[k + OFF], x, BX[k]); BX[k] = x; }
+    }
+}
+
+// in-place exclusive prefix sum of h[0..n) (n <= THREADS * (E + 1)); returns nothing, h[i] <- sum_{j<i} h[j]
+template <int THREADS, int E>
+__device__ __forceinline__ void block_exclusive_sum(uint32_t* __restrict__ h, const int n, uint32_t* __restrict__ wsum)
+{
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int per = (n + THREADS - 1) / THREADS;          // <= E + 1
+    const int i0  = min(n, tid * per), i1 = min(n, i0 + per);
+    uint32_t run = 0;
+    for (int i = i0; i < i1; i++) run += h[i];
+    uint32_t incl = run;
+    #pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        uint32_t t = __shfl_up_sync(FULL, incl, off);
+        if (lane >= off) incl += t;
+    }
+    __syncthreads();
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    uint32_t pre = incl - run;
+    for (int w = 0; w < warp; w++) pre += wsum[w];
+    for (int i = i0; i < i1; i++) { uint32_t c = h[i]; h[i] = pre; pre += c; }
 }
 
 __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const int n, const float x) {
@@ -140,21 +175,22 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
     while (lo < hi) { int mid = (lo + hi) >> 1; if (a[mid] < x) lo = mid + 1; else hi = mid; }
     return lo;
 }
-__device__ __forceinline__ int lower_bound_u(const uint32_t* __restrict__ a, const int n, const uint32_t x) {
-    int lo = 0, hi = n;
-    while (lo < hi) { int mid = (lo + hi) >> 1; if (a[mid] < x) lo = mid + 1; else hi = mid; }
-    return lo;
-}
 
 // ------------------------------------------------------------------ the kernel
+// Phases: (1) radix sort of the keys; (2) per-key decays and the scalar scans, each thread on a
+// contiguous run of keys with the decays in registers; (3) the queries are not sorted by value:
+// each is ranked against the sorted keys by binary search and the records are ordered by rank
+// with a counting sort (shared-memory histogram over the N + 1 ranks, exclusive scan, atomic
+// cursor), which also yields mstart for free. Queries of equal rank come out in arbitrary order,
+// which the walk does not care about.
 template <int THREADS, int E>
 __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
 {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);
-    float*    xs   = reinterpret_cast<float*>(skey + CAP);
+    uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);        // sort buffer, later the rank histogram (CAP + 1 + pad)
+    float*    xs   = reinterpret_cast<float*>(skey + CAP + 32);    // sorted keys
     uint32_t* cnt  = reinterpret_cast<uint32_t*>(xs + CAP);
     uint32_t* base = cnt + W * 256;
     uint32_t* wsum = base + 256;
@@ -175,90 +211,122 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
     float*    su0    = a.su0 ? a.su0 + (long long)seg * (N + 1) : nullptr;
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
 
-    uint32_t key[E], idx[E];
-
-    // ---- keys
-    load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
-    block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
+    // ---- (1) keys
+    {
+        uint32_t key[E], idx[E];
+        load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
+        block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
+    }
     for (int j = tid; j < NP; j += THREADS) {
         if (j < N) xs[j] = key2f(skey[j]);
         xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     }
     __syncthreads();
 
-    auto dec = [&](int j) -> float { return (j > 0 && j < N) ? expf(-(xs[j] - xs[j - 1])) : 0.0f; };   // a_j
-    if (a.mode != MODE_SGN) {
-        for (int j = tid; j < NP + KB; j += THREADS) {
-            float val;
-            if (a.mode == MODE_LAPLACE) val = j < N ? dec(j) : 1.0f;
-            else                        val = j < N ? xs[j] : 0.0f;
-            xval[j] = val;
-        }
-    }
-
-    // ---- scalar scans over the sorted keys (results in su0 / su1, read back per query below)
-    if (a.scal == SCAL_UNIT && a.mode == MODE_LAPLACE) {
-        // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
-        block_affine_scan<THREADS>(N, wa, wb,
-            [&](int i, float& A, float& B) { A = dec(i); B = 1.0f; },
-            [&](int i, float x) { su0[i] = x; });
-        block_affine_scan<THREADS>(N, wa, wb,
-            [&](int i, float& A, float& B) { A = dec(N - i); B = 1.0f; },      // position i <-> key N-1-i, decay a_{j+1}
-            [&](int i, float x) { su1[N - 1 - i] = x; });
-    } else if (a.scal == SCAL_UNIT) {
-        // su0[j] = sum_{i<=j} k_i
-        block_affine_scan<THREADS>(N, wa, wb,
-            [&](int i, float& A, float& B) { A = 1.0f; B = xs[i]; },
-            [&](int i, float x) { su0[i] = x; });
-    } else if (a.scal == SCAL_PREFIX) {
-        const float* us = a.us + (long long)p * N;
-        block_affine_scan<THREADS>(N, wa, wb,
-            [&](int i, float& A, float& B) { A = 1.0f; B = us[sidx[i]]; },
-            [&](int i, float x) { su0[i] = x; });
-    }
-    __syncthreads();          // sidx / skey are about to be reused; the su arrays are complete
-
-    // ---- queries
-    load_segment<THREADS, E>(a.y + (long long)seg * M, M, key, idx);
-    block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
-
-    for (int m = tid; m < M; m += THREADS) {
-        const float    y   = key2f(skey[m]);
-        const uint32_t row = sidx[m];
-        const int      r   = lower_bound_f(xs, N, y);
-        float e0 = 0.0f, e1 = 0.0f;
+    // ---- (2) per-key scalars; my run of keys is [i0, i0 + cnt)
+    {
+        const int per = (N + THREADS - 1) / THREADS;              // <= E
+        const int i0  = min(N, tid * per), cntk = min(N, i0 + per) - i0;
+        float dk[E + 1];                                          // dk[k] = decay a_{i0+k} = exp(-(k_j - k_{j-1})), a_0 = 0, a_N = 0
         if (a.mode == MODE_LAPLACE) {
-            e0 = r > 0 ? expf(-(y - xs[r - 1])) : 0.0f;
-            e1 = r < N ? expf(-(xs[r] - y)) : 0.0f;
-            if (a.scal == SCAL_UNIT) {
-                float u = (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f);
-                atomicAdd(a.out_u + (long long)p * M + row, u);
+            #pragma unroll
+            for (int k = 0; k <= E; k++) {
+                const int j = i0 + k;
+                dk[k] = (k <= cntk && j > 0 && j < N) ? expf(-(xs[j] - xs[j - 1])) : 0.0f;
             }
-        } else {
-            if (a.mode == MODE_ABS) e0 = 2.0f * y;
-            if (a.scal == SCAL_UNIT) {
-                float pk = r > 0 ? su0[r - 1] : 0.0f;
-                atomicAdd(a.out_u + (long long)p * M + row, 2.0f * (y * (float)r - pk));
-            } else if (a.scal == SCAL_RANK) {
-                e1 = a.uq[(long long)p * M + row] * (2.0f * (float)r - (float)N);
-            } else if (a.scal == SCAL_PREFIX) {
-                e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
-            }
+            #pragma unroll
+            for (int k = 0; k < E; k++) if (k < cntk) xval[i0 + k] = dk[k];
+            for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
+        } else if (a.mode == MODE_ABS) {
+            for (int j = tid; j < NP + KB; j += THREADS) xval[j] = j < N ? xs[j] : 0.0f;
         }
-        yrec[m] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), row, (uint32_t)r);
-        skey[m] = (uint32_t)r;                    // only this thread ever reads skey[m] above
+        if (a.scal == SCAL_UNIT && a.mode == MODE_LAPLACE) {
+            // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
+            float bx[E];
+            #pragma unroll
+            for (int k = 0; k < E; k++) bx[k] = 1.0f;
+            block_affine_scan<THREADS, E, false, 0>(cntk, dk, bx, wa, wb);
+            #pragma unroll
+            for (int k = 0; k < E; k++) if (k < cntk) su0[i0 + k] = bx[k];
+            // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
+            #pragma unroll
+            for (int k = 0; k < E; k++) bx[k] = 1.0f;
+            block_affine_scan<THREADS, E, true, 1>(cntk, dk, bx, wa, wb);
+            #pragma unroll
+            for (int k = 0; k < E; k++) if (k < cntk) su1[i0 + k] = bx[k];
+        } else if (a.scal == SCAL_UNIT || a.scal == SCAL_PREFIX) {
+            // su0[j] = sum_{i<=j} k_i   or   sum_{i<=j} us[row of key i]
+            const float* us = a.scal == SCAL_PREFIX ? a.us + (long long)p * N : nullptr;
+            float bx[E];
+            #pragma unroll
+            for (int k = 0; k <= E; k++) dk[k] = 1.0f;
+            #pragma unroll
+            for (int k = 0; k < E; k++) bx[k] = k < cntk ? (us ? us[sidx[i0 + k]] : xs[i0 + k]) : 0.0f;
+            block_affine_scan<THREADS, E, false, 0>(cntk, dk, bx, wa, wb);
+            #pragma unroll
+            for (int k = 0; k < E; k++) if (k < cntk) su0[i0 + k] = bx[k];
+        }
+    }
+    __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
+
+    // ---- (3) queries: rank, counting sort by rank, records
+    uint32_t* hist = skey;                                         // N + 1 bins
+    for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
+    __syncthreads();
+    const float* ysrc = a.y + (long long)seg * M;
+    float    yv[E];
+    uint32_t rk[E];
+    #pragma unroll
+    for (int s = 0; s < E; s++) {
+        const int m = tid + s * THREADS;
+        if (m < M) {
+            yv[s] = ysrc[m];
+            rk[s] = (uint32_t)lower_bound_f(xs, N, yv[s]);
+            atomicAdd(&hist[rk[s]], 1u);
+        }
+    }
+    __syncthreads();
+    block_exclusive_sum<THREADS, E>(hist, N + 1, wsum);
+    __syncthreads();
+    for (int b = tid; b <= NBK; b += THREADS) mstart[b] = b == NBK ? (uint32_t)M : hist[b * KB];     // b*KB <= N for b < NBK
+    __syncthreads();
+    #pragma unroll
+    for (int s = 0; s < E; s++) {
+        const int m = tid + s * THREADS;
+        if (m < M) {
+            const float y = yv[s];
+            const int   r = (int)rk[s];
+            float e0 = 0.0f, e1 = 0.0f;
+            if (a.mode == MODE_LAPLACE) {
+                e0 = r > 0 ? expf(-(y - xs[r - 1])) : 0.0f;
+                e1 = r < N ? expf(-(xs[r] - y)) : 0.0f;
+                if (a.scal == SCAL_UNIT) {
+                    float u = (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f);
+                    atomicAdd(a.out_u + (long long)p * M + m, u);
+                }
+            } else {
+                if (a.mode == MODE_ABS) e0 = 2.0f * y;
+                if (a.scal == SCAL_UNIT) {
+                    float pk = r > 0 ? su0[r - 1] : 0.0f;
+                    atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - pk));
+                } else if (a.scal == SCAL_RANK) {
+                    e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
+                } else if (a.scal == SCAL_PREFIX) {
+                    e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
+                }
+            }
+            const uint32_t pos = atomicAdd(&hist[r], 1u);
+            yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
+        }
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
-    __syncthreads();
-    for (int b = tid; b <= NBK; b += THREADS)
-        mstart[b] = b == NBK ? (uint32_t)M : (uint32_t)lower_bound_u(skey, M, (uint32_t)(b * KB));
 }
 
 template <int THREADS, int E>
 static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
-    const size_t smem = (size_t)CAP * 4 * 2 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
+    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
     auto kern = sort_rank_small<THREADS, E>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

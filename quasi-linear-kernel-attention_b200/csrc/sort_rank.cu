@@ -11,10 +11,18 @@
 
 namespace qlka {
 
+// Optional per-phase cycle stamps of CTA 0 (development aid; compiled out unless QLKA_PHASE_TIMING is defined).
+#ifdef QLKA_PHASE_TIMING
+__device__ long long g_phase_clock[16];
+#define PHASE_STAMP(i) do { __syncthreads(); if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); } while (0)
+#else
+#define PHASE_STAMP(i) do {} while (0)
+#endif
+
 // ------------------------------------------------------------------ block radix sort
 // Elements are held in registers, E per thread, in warp-blocked order: the element at
 // array position warp*32*E + s*32 + lane sits in slot s of that lane. One pass ranks each
-// element among equal digits of its own warp (match_any + per-warp counters, processed in
+// element among equal digits of its own warp (ballots + per-warp counters, processed in
 // array order so the pass is stable), scans the counters digit-major, and scatters through
 // shared memory.
 template <int THREADS, int E>
@@ -39,7 +47,12 @@ __device__ __forceinline__ void block_radix_sort(
         #pragma unroll
         for (int s = 0; s < E; s++) {
             const uint32_t d      = (key[s] >> shift) & 255u;
-            const uint32_t peers  = __match_any_sync(FULL, d);
+            uint32_t       peers  = FULL;                  // lanes holding the same digit: eight ballots
+            #pragma unroll                                 // (match.any has the same result but a far lower rate)
+            for (int bit = 0; bit < 8; bit++) {
+                const uint32_t vote = __ballot_sync(FULL, (d >> bit) & 1u);
+                peers &= ((d >> bit) & 1u) ? vote : ~vote;
+            }
             const int      leader = __ffs(peers) - 1;
             uint32_t       old    = 0;
             if (lane == leader) { old = mycnt[d]; mycnt[d] = old + __popc(peers); }
@@ -170,9 +183,14 @@ __device__ __forceinline__ void block_exclusive_sum(uint32_t* __restrict__ h, co
     for (int i = i0; i < i1; i++) { uint32_t c = h[i]; h[i] = pre; pre += c; }
 }
 
+// The sorted keys sit in shared memory with one word of padding after every 32: a binary search
+// over a power-of-two array otherwise probes addresses that are multiples of a large power of two,
+// i.e. one bank, in its first ten steps.
+__device__ __forceinline__ int skew(const int i) { return i + (i >> 5); }
+
 __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const int n, const float x) {
     int lo = 0, hi = n;
-    while (lo < hi) { int mid = (lo + hi) >> 1; if (a[mid] < x) lo = mid + 1; else hi = mid; }
+    while (lo < hi) { int mid = (lo + hi) >> 1; if (a[skew(mid)] < x) lo = mid + 1; else hi = mid; }
     return lo;
 }
 
@@ -191,7 +209,7 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);        // sort buffer, later the rank histogram (CAP + 1 + pad)
     float*    xs   = reinterpret_cast<float*>(skey + CAP + 32);    // sorted keys
-    uint32_t* cnt  = reinterpret_cast<uint32_t*>(xs + CAP);
+    uint32_t* cnt  = reinterpret_cast<uint32_t*>(xs + CAP + CAP / 32);
     uint32_t* base = cnt + W * 256;
     uint32_t* wsum = base + 256;
     float*    wa   = reinterpret_cast<float*>(wsum + 32);
@@ -211,64 +229,79 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
     float*    su0    = a.su0 ? a.su0 + (long long)seg * (N + 1) : nullptr;
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
 
+    PHASE_STAMP(0);
     // ---- (1) keys
     {
         uint32_t key[E], idx[E];
         load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
         block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
     }
+    PHASE_STAMP(1);
     for (int j = tid; j < NP; j += THREADS) {
-        if (j < N) xs[j] = key2f(skey[j]);
+        if (j < N) xs[skew(j)] = key2f(skey[j]);
         xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     }
     __syncthreads();
 
-    // ---- (2) per-key scalars; my run of keys is [i0, i0 + cnt)
+    PHASE_STAMP(2);
+    // ---- (2) per-key scalars; my run of keys is [i0, i0 + cntk). The run length is odd so that the
+    // strided shared-memory accesses below are bank-conflict free; results leave through a staging
+    // buffer (the idle sort buffer) so that the global stores are coalesced.
     {
-        const int per = (N + THREADS - 1) / THREADS;              // <= E
+        constexpr int R = E + 1;                                  // run capacity
+        const int per = ((N + THREADS - 1) / THREADS) | 1;        // <= R
         const int i0  = min(N, tid * per), cntk = min(N, i0 + per) - i0;
-        float dk[E + 1];                                          // dk[k] = decay a_{i0+k} = exp(-(k_j - k_{j-1})), a_0 = 0, a_N = 0
+        float*    stage = reinterpret_cast<float*>(skey);
+        auto flush = [&](const float (&val)[R], float* __restrict__ dst) {
+            __syncthreads();
+            #pragma unroll
+            for (int k = 0; k < R; k++) if (k < cntk) stage[i0 + k] = val[k];
+            __syncthreads();
+            for (int j = tid; j < N; j += THREADS) dst[j] = stage[j];
+        };
+        float dk[R + 1];                                          // dk[k] = decay a_{i0+k} = exp(-(k_j - k_{j-1})), a_0 = 0, a_N = 0
         if (a.mode == MODE_LAPLACE) {
             #pragma unroll
-            for (int k = 0; k <= E; k++) {
+            for (int k = 0; k <= R; k++) {
                 const int j = i0 + k;
-                dk[k] = (k <= cntk && j > 0 && j < N) ? expf(-(xs[j] - xs[j - 1])) : 0.0f;
+                dk[k] = (k <= cntk && j > 0 && j < N) ? expf(-(xs[skew(j)] - xs[skew(j - 1)])) : 0.0f;
             }
+            float bx[R];
             #pragma unroll
-            for (int k = 0; k < E; k++) if (k < cntk) xval[i0 + k] = dk[k];
+            for (int k = 0; k < R; k++) bx[k] = dk[k];
+            flush(bx, xval);
             for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
-        } else if (a.mode == MODE_ABS) {
-            for (int j = tid; j < NP + KB; j += THREADS) xval[j] = j < N ? xs[j] : 0.0f;
-        }
-        if (a.scal == SCAL_UNIT && a.mode == MODE_LAPLACE) {
-            // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
-            float bx[E];
-            #pragma unroll
-            for (int k = 0; k < E; k++) bx[k] = 1.0f;
-            block_affine_scan<THREADS, E, false, 0>(cntk, dk, bx, wa, wb);
-            #pragma unroll
-            for (int k = 0; k < E; k++) if (k < cntk) su0[i0 + k] = bx[k];
-            // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
-            #pragma unroll
-            for (int k = 0; k < E; k++) bx[k] = 1.0f;
-            block_affine_scan<THREADS, E, true, 1>(cntk, dk, bx, wa, wb);
-            #pragma unroll
-            for (int k = 0; k < E; k++) if (k < cntk) su1[i0 + k] = bx[k];
-        } else if (a.scal == SCAL_UNIT || a.scal == SCAL_PREFIX) {
-            // su0[j] = sum_{i<=j} k_i   or   sum_{i<=j} us[row of key i]
-            const float* us = a.scal == SCAL_PREFIX ? a.us + (long long)p * N : nullptr;
-            float bx[E];
-            #pragma unroll
-            for (int k = 0; k <= E; k++) dk[k] = 1.0f;
-            #pragma unroll
-            for (int k = 0; k < E; k++) bx[k] = k < cntk ? (us ? us[sidx[i0 + k]] : xs[i0 + k]) : 0.0f;
-            block_affine_scan<THREADS, E, false, 0>(cntk, dk, bx, wa, wb);
-            #pragma unroll
-            for (int k = 0; k < E; k++) if (k < cntk) su0[i0 + k] = bx[k];
+            if (a.scal == SCAL_UNIT) {
+                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
+                #pragma unroll
+                for (int k = 0; k < R; k++) bx[k] = 1.0f;
+                block_affine_scan<THREADS, R, false, 0>(cntk, dk, bx, wa, wb);
+                flush(bx, su0);
+                // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
+                #pragma unroll
+                for (int k = 0; k < R; k++) bx[k] = 1.0f;
+                block_affine_scan<THREADS, R, true, 1>(cntk, dk, bx, wa, wb);
+                flush(bx, su1);
+            }
+        } else {
+            if (a.mode == MODE_ABS)
+                for (int j = tid; j < NP + KB; j += THREADS) xval[j] = j < N ? xs[skew(j)] : 0.0f;
+            if (a.scal == SCAL_UNIT || a.scal == SCAL_PREFIX) {
+                // su0[j] = sum_{i<=j} k_i   or   sum_{i<=j} us[row of key i]
+                const float* us = a.scal == SCAL_PREFIX ? a.us + (long long)p * N : nullptr;
+                float bx[R];
+                #pragma unroll
+                for (int k = 0; k <= R; k++) dk[k] = 1.0f;
+                #pragma unroll
+                for (int k = 0; k < R; k++) bx[k] = k < cntk ? (us ? us[sidx[i0 + k]] : xs[skew(i0 + k)]) : 0.0f;
+                block_affine_scan<THREADS, R, false, 0>(cntk, dk, bx, wa, wb);
+                flush(bx, su0);
+            }
         }
     }
     __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
 
+    PHASE_STAMP(3);
     // ---- (3) queries: rank, counting sort by rank, records
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
@@ -282,13 +315,17 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
         if (m < M) {
             yv[s] = ysrc[m];
             rk[s] = (uint32_t)lower_bound_f(xs, N, yv[s]);
-            atomicAdd(&hist[rk[s]], 1u);
         }
     }
+    PHASE_STAMP(7);
+    #pragma unroll
+    for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rk[s]], 1u);
     __syncthreads();
+    PHASE_STAMP(4);
     block_exclusive_sum<THREADS, E>(hist, N + 1, wsum);
     __syncthreads();
     for (int b = tid; b <= NBK; b += THREADS) mstart[b] = b == NBK ? (uint32_t)M : hist[b * KB];     // b*KB <= N for b < NBK
+    PHASE_STAMP(5);
     __syncthreads();
     #pragma unroll
     for (int s = 0; s < E; s++) {
@@ -298,8 +335,8 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
             const int   r = (int)rk[s];
             float e0 = 0.0f, e1 = 0.0f;
             if (a.mode == MODE_LAPLACE) {
-                e0 = r > 0 ? expf(-(y - xs[r - 1])) : 0.0f;
-                e1 = r < N ? expf(-(xs[r] - y)) : 0.0f;
+                e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
+                e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
                 if (a.scal == SCAL_UNIT) {
                     float u = (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f);
                     atomicAdd(a.out_u + (long long)p * M + m, u);
@@ -320,13 +357,20 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
         }
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
+    PHASE_STAMP(6);
 }
+
+#ifdef QLKA_PHASE_TIMING
+extern "C" int qlka_debug_phase_clocks(long long* out16) {
+    return (int)cudaMemcpyFromSymbol(out16, g_phase_clock, sizeof(long long) * 16);
+}
+#endif
 
 template <int THREADS, int E>
 static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
-    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
+    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
     auto kern = sort_rank_small<THREADS, E>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

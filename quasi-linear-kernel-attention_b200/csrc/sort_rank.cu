@@ -194,6 +194,29 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
     return lo;
 }
 
+// One query's record into its staging slot, plus its share of the unit column or its scalar term.
+__device__ __noinline__ void make_record(const SortArgs& a, const float* __restrict__ xs, const float* __restrict__ su0s,
+                                         const float* __restrict__ su0, const float* __restrict__ su1,
+                                         const float* __restrict__ ysrc, uint4* __restrict__ slot,
+                                         const int p, const int m, const int r)
+{
+    const int   N = a.N, M = a.M;
+    const float y = ysrc[m];
+    float e0 = 0.0f, e1 = 0.0f;
+    if (a.mode == MODE_LAPLACE) {
+        e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
+        e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
+        if (a.scal == SCAL_UNIT)
+            atomicAdd(a.out_u + (long long)p * M + m, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+    } else {
+        if (a.mode == MODE_ABS) e0 = 2.0f * y;
+        if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
+        else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
+        else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
+    }
+    *slot = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
+}
+
 // ------------------------------------------------------------------ the kernel
 // Phases: (1) radix sort of the keys; (2) per-key decays and the scalar scans, each thread on a
 // contiguous run of keys with the decays in registers; (3) the queries are not sorted by value:
@@ -202,19 +225,20 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 // cursor), which also yields mstart for free. Queries of equal rank come out in arbitrary order,
 // which the walk does not care about.
 template <int THREADS, int E>
-__global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
+__global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
 {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);        // sort buffer, later the rank histogram (CAP + 1 + pad)
     float*    xs   = reinterpret_cast<float*>(skey + CAP + 32);    // sorted keys
-    uint32_t* cnt  = reinterpret_cast<uint32_t*>(xs + CAP + CAP / 32);
-    uint32_t* base = cnt + W * 256;
+    uint32_t* base = reinterpret_cast<uint32_t*>(xs + CAP + CAP / 32);
     uint32_t* wsum = base + 256;
     float*    wa   = reinterpret_cast<float*>(wsum + 32);
     float*    wb   = wa + 32;
-    uint16_t* sidx = reinterpret_cast<uint16_t*>(wb + 32);
+    uint32_t* cnt  = reinterpret_cast<uint32_t*>(wb + 32);          // per-warp digit counters ...
+    uint16_t* sidx = reinterpret_cast<uint16_t*>(cnt + W * 256);    // ... and the index payload; together >= 4 * CAP bytes
+    float*    su0s = reinterpret_cast<float*>(cnt);                 // Laplace: forward unit scan, once both are idle
 
     const int tid = threadIdx.x;
     const int seg = blockIdx.x;
@@ -276,7 +300,8 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
                 #pragma unroll
                 for (int k = 0; k < R; k++) bx[k] = 1.0f;
                 block_affine_scan<THREADS, R, false, 0>(cntk, dk, bx, wa, wb);
-                flush(bx, su0);
+                #pragma unroll
+                for (int k = 0; k < R; k++) if (k < cntk) su0s[i0 + k] = bx[k];     // stays in shared memory
                 // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
                 #pragma unroll
                 for (int k = 0; k < R; k++) bx[k] = 1.0f;
@@ -307,19 +332,32 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();
     const float* ysrc = a.y + (long long)seg * M;
-    float    yv[E];
-    uint32_t rk[E];
+    uint32_t rp[E];                                   // rank, later rank | position << 16 (both <= 16384)
+    // branch-free binary search, four queries in flight per thread
     #pragma unroll
-    for (int s = 0; s < E; s++) {
-        const int m = tid + s * THREADS;
-        if (m < M) {
-            yv[s] = ysrc[m];
-            rk[s] = (uint32_t)lower_bound_f(xs, N, yv[s]);
+    for (int s0 = 0; s0 < E; s0 += 4) {
+        int   pos4[4];
+        float y4[4];
+        #pragma unroll
+        for (int t = 0; t < 4; t++) {
+            const int m = tid + (s0 + t) * THREADS;
+            y4[t]   = m < M ? ysrc[m] : 0.0f;
+            pos4[t] = 0;
         }
+        #pragma unroll
+        for (int step = CAP; step >= 1; step >>= 1) {
+            #pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const int probe = pos4[t] + step;
+                if (probe <= N && xs[skew(probe - 1)] < y4[t]) pos4[t] = probe;
+            }
+        }
+        #pragma unroll
+        for (int t = 0; t < 4; t++) rp[s0 + t] = (uint32_t)pos4[t];     // number of keys strictly below the query
     }
     PHASE_STAMP(7);
     #pragma unroll
-    for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rk[s]], 1u);
+    for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rp[s]], 1u);
     __syncthreads();
     PHASE_STAMP(4);
     block_exclusive_sum<THREADS, E>(hist, N + 1, wsum);
@@ -328,33 +366,25 @@ __global__ void __launch_bounds__(THREADS) sort_rank_small(const SortArgs a)
     PHASE_STAMP(5);
     __syncthreads();
     #pragma unroll
-    for (int s = 0; s < E; s++) {
-        const int m = tid + s * THREADS;
-        if (m < M) {
-            const float y = yv[s];
-            const int   r = (int)rk[s];
-            float e0 = 0.0f, e1 = 0.0f;
-            if (a.mode == MODE_LAPLACE) {
-                e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
-                e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
-                if (a.scal == SCAL_UNIT) {
-                    float u = (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f);
-                    atomicAdd(a.out_u + (long long)p * M + m, u);
-                }
-            } else {
-                if (a.mode == MODE_ABS) e0 = 2.0f * y;
-                if (a.scal == SCAL_UNIT) {
-                    float pk = r > 0 ? su0[r - 1] : 0.0f;
-                    atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - pk));
-                } else if (a.scal == SCAL_RANK) {
-                    e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
-                } else if (a.scal == SCAL_PREFIX) {
-                    e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
-                }
-            }
-            const uint32_t pos = atomicAdd(&hist[r], 1u);
-            yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
+    for (int s = 0; s < E; s++)
+        if (tid + s * THREADS < M) rp[s] |= atomicAdd(&hist[rp[s]], 1u) << 16;       // final position of the record
+    __syncthreads();
+    // the histogram is spent: its memory stages the records, a chunk of positions at a time, so that
+    // they reach global memory as full coalesced lines
+    uint4* stage4 = reinterpret_cast<uint4*>(skey);
+    constexpr int CHUNK = CAP / 4;                    // records per round (16 bytes each: CAP * 4 bytes of staging)
+    for (int c0 = 0; c0 < M; c0 += CHUNK) {
+        #pragma unroll
+        for (int s = 0; s < E; s++) {
+            const int      m   = tid + s * THREADS;
+            const uint32_t pos = rp[s] >> 16;
+            if (m < M && pos >= (uint32_t)c0 && pos < (uint32_t)(c0 + CHUNK))
+                make_record(a, xs, su0s, su0, su1, ysrc, stage4 + (pos - c0), p, m, (int)(rp[s] & 0xffffu));
         }
+        __syncthreads();
+        const int nrec = min(CHUNK, M - c0);
+        for (int i = tid; i < nrec; i += THREADS) yrec[c0 + i] = stage4[i];
+        __syncthreads();
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
     PHASE_STAMP(6);

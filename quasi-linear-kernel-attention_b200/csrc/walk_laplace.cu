@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
     constexpr int CW      = LPS * CPL;               // channel capacity of a stream
     extern __shared__ __align__(16) float4 smem[];
     float4* ring  = smem;                                                    // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
-    uint4*  qs_all = reinterpret_cast<uint4*>(ring + RING_DEPTH * ring_slot_f4<CPL>());   // [STREAMS][RING_DEPTH][LPS]
+    uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());   // [STREAMS][RING_DEPTH][LPS]
     float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);       // [STREAMS][RING_DEPTH][SX_STRIDE]
     // stream aggregates live in the ring's memory between the two passes
     float (*sF)[CW] = reinterpret_cast<float (*)[CW]>(ring);                 // forward aggregate  -> incoming prefix state
@@ -50,10 +50,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
 
     Feeder<LPS, CPL> f;
-    f.ring = ring + tid;
-    f.qs   = qs_all + st * RING_DEPTH * LPS;
-    f.sxs  = sx_all + st * RING_DEPTH * SX_STRIDE;
-    f.C4 = C4; f.N = N; f.ln = ln; f.gmask = gmask; f.with_x = true;
+    f.ring_s = smem_u32(ring + tid);
+    f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
+    f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = true;
 
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
@@ -94,9 +94,8 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                 cp_async_wait<RING_DEPTH - 1>();
                 __syncwarp(gmask);
                 float av[KB + 1];
-                const float* sx = f.sxs + cur * SX_STRIDE;
-                #pragma unroll
-                for (int i = 0; i <= KB; i++) av[i] = sx[i];
+                uint32_t m_lo, m_hi;
+                f.read_scalars(cur, av, m_lo, m_hi);
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
                 #pragma unroll
@@ -189,10 +188,9 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                 cp_async_wait<RING_DEPTH - 1>();
                 __syncwarp(gmask);
                 float av[KB + 1];
-                const float* sx = f.sxs + cur * SX_STRIDE;
-                #pragma unroll
-                for (int i = 0; i <= KB; i++) av[i] = sx[i];
-                const uint32_t m_lo = __float_as_uint(sx[9]), cnt = __float_as_uint(sx[10]) - m_lo;
+                uint32_t m_lo, m_hi;
+                f.read_scalars(cur, av, m_lo, m_hi);
+                const uint32_t cnt = m_hi - m_lo;
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
 
@@ -212,30 +210,46 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) laplace_walk
                         L.x[c] = fmaf(av[i], L.x[c], t2);
                     }
                 }
-                // the block's queries, in rank order: the first LPS from the staged slot, any others from memory
-                const uint4* qslot = f.qs + cur * LPS;
-                auto fetch = [&](uint32_t n) -> uint4 {
-                    if (n >= cnt) return make_uint4(0u, 0u, 0u, 0xffffffffu);
-                    return n < (uint32_t)LPS ? qslot[n] : __ldg(f.yrec + m_lo + n);
+                // the block's queries, in rank order
+                auto emit = [&](const uint4 rec, const Vec<CPL>& Lq, const Vec<CPL>& Rq) {
+                    const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
+                    if (on) {
+                        float* o = out + (size_t)rec.z * C4;
+                        #pragma unroll
+                        for (int c = 0; c < CPL; c += 4)
+                            red_add4(o + c,
+                                     fmaf(e0, Lq.x[c],     e1 * Rq.x[c]),
+                                     fmaf(e0, Lq.x[c + 1], e1 * Rq.x[c + 1]),
+                                     fmaf(e0, Lq.x[c + 2], e1 * Rq.x[c + 2]),
+                                     fmaf(e0, Lq.x[c + 3], e1 * Rq.x[c + 3]));
+                    }
                 };
-                uint32_t n   = 0;
-                uint4    rec = fetch(0);
-                #pragma unroll
-                for (int i = 0; i < KB; i++) {
-                    while (rec.w == (uint32_t)(j0 + i)) {
-                        const uint4 nxt = fetch(++n);
-                        const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
-                        if (on) {
-                            float* o = out + (size_t)rec.z * C4;
-                            #pragma unroll
-                            for (int c = 0; c < CPL; c += 4)
-                                red_add4(o + c,
-                                         fmaf(e0, v[i].x[c],     e1 * Rb[i].x[c]),
-                                         fmaf(e0, v[i].x[c + 1], e1 * Rb[i].x[c + 1]),
-                                         fmaf(e0, v[i].x[c + 2], e1 * Rb[i].x[c + 2]),
-                                         fmaf(e0, v[i].x[c + 3], e1 * Rb[i].x[c + 3]));
+                if (cnt < (uint32_t)LPS) {
+                    // usual case: every record of the block and a closing sentinel sit in the staged slot
+                    uint32_t qa  = f.qs_s + cur * LPS * 16;
+                    uint4    rec = lds128u(qa);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) {
+                        while (rec.w == (uint32_t)(j0 + i)) {
+                            qa += 16;
+                            const uint4 nxt = lds128u(qa);
+                            emit(rec, v[i], Rb[i]);
+                            rec = nxt;
                         }
-                        rec = nxt;
+                    }
+                } else {
+                    // more queries than the slot holds: read them from memory
+                    const uint4* yp  = f.yrec + m_lo;
+                    uint32_t     n   = 0;
+                    uint4        rec = __ldg(yp);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) {
+                        while (n < cnt && rec.w == (uint32_t)(j0 + i)) {
+                            ++n;
+                            const uint4 nxt = __ldg(yp + n);        // at most the segment's sentinel
+                            emit(rec, v[i], Rb[i]);
+                            rec = nxt;
+                        }
                     }
                 }
                 cur = ring_next(cur);

@@ -27,7 +27,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
     constexpr bool WITH_K  = EMIT == EMIT_ROWS;
     extern __shared__ __align__(16) float4 smem[];
     float4* ring   = smem;
-    uint4*  qs_all = reinterpret_cast<uint4*>(ring + RING_DEPTH * ring_slot_f4<CPL>());
+    uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
     float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);
     float (*sV)[CW] = reinterpret_cast<float (*)[CW]>(ring);     // stream sums, in the ring's memory between the passes
     float (*sK)[CW] = sV + STREAMS;
@@ -43,10 +43,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
 
     Feeder<LPS, CPL> f;
-    f.ring = ring + tid;
-    f.qs   = qs_all + st * RING_DEPTH * LPS;
-    f.sxs  = sx_all + st * RING_DEPTH * SX_STRIDE;
-    f.C4 = C4; f.N = N; f.ln = ln; f.gmask = gmask; f.with_x = WITH_K;
+    f.ring_s = smem_u32(ring + tid);
+    f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
+    f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = WITH_K;
 
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
@@ -80,12 +80,11 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                 if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
                 if (t + 3 < nblk) f.prefetch_index(b + 3);
                 cp_async_wait<RING_DEPTH - 1>();
-                float kv[KB];
+                float kv[KB + 1];
                 if (WITH_K) {
                     __syncwarp(gmask);
-                    const float* sx = f.sxs + cur * SX_STRIDE;
-                    #pragma unroll
-                    for (int i = 0; i < KB; i++) kv[i] = sx[i];
+                    uint32_t m_lo, m_hi;
+                    f.read_scalars(cur, kv, m_lo, m_hi);
                 }
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
@@ -154,13 +153,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                 if (t + 3 < nblk) f.prefetch_index(b + 3);
                 cp_async_wait<RING_DEPTH - 1>();
                 __syncwarp(gmask);
-                const float* sx = f.sxs + cur * SX_STRIDE;
-                float kv[KB];
-                if (WITH_K) {
-                    #pragma unroll
-                    for (int i = 0; i < KB; i++) kv[i] = sx[i];
-                }
-                const uint32_t m_lo = __float_as_uint(sx[9]), cnt = __float_as_uint(sx[10]) - m_lo;
+                float kv[KB + 1];
+                uint32_t m_lo, m_hi;
+                f.read_scalars(cur, kv, m_lo, m_hi);      // (the key values are only staged and used by EMIT_ROWS)
+                const uint32_t cnt = m_hi - m_lo;
                 Vec<CPL> v[KB], kb[WITH_K ? KB : 1];
                 f.read_rows(cur, j0, v);
                 // prefix states before each key, in place of the rows
@@ -174,47 +170,61 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t2, PK.x[c]); }
                     }
                 }
-                const uint4* qslot = f.qs + cur * LPS;
-                auto fetch = [&](uint32_t n) -> uint4 {
-                    if (n >= cnt) return make_uint4(0u, 0u, 0u, 0xffffffffu);
-                    return n < (uint32_t)LPS ? qslot[n] : __ldg(f.yrec + m_lo + n);
-                };
-                uint32_t n   = 0;
-                uint4    rec = fetch(0);
-                #pragma unroll
-                for (int i = 0; i < KB; i++) {
-                    while (rec.w == (uint32_t)(j0 + i)) {
-                        const uint4 nxt = fetch(++n);
-                        if (EMIT == EMIT_ROWS) {
-                            const float e0 = __uint_as_float(rec.x);
-                            if (on) {
-                                float* o = out + (size_t)rec.z * C4;
-                                #pragma unroll
-                                for (int c = 0; c < CPL; c += 4)
-                                    red_add4(o + c,
-                                             fmaf(e0, v[i].x[c],     -2.0f * kb[WITH_K ? i : 0].x[c]),
-                                             fmaf(e0, v[i].x[c + 1], -2.0f * kb[WITH_K ? i : 0].x[c + 1]),
-                                             fmaf(e0, v[i].x[c + 2], -2.0f * kb[WITH_K ? i : 0].x[c + 2]),
-                                             fmaf(e0, v[i].x[c + 3], -2.0f * kb[WITH_K ? i : 0].x[c + 3]));
-                            }
-                        } else {
-                            float acc = 0.0f;
-                            if (lane_on) {
-                                const float* gr = g + (size_t)rec.z * C4;
-                                #pragma unroll
-                                for (int c = 0; c < CPL; c += 4) {
-                                    const float4 t4 = ldg4(gr + c);
-                                    acc = fmaf(t4.x, fmaf(2.0f, v[i].x[c],     -wt.x[c]),     acc);
-                                    acc = fmaf(t4.y, fmaf(2.0f, v[i].x[c + 1], -wt.x[c + 1]), acc);
-                                    acc = fmaf(t4.z, fmaf(2.0f, v[i].x[c + 2], -wt.x[c + 2]), acc);
-                                    acc = fmaf(t4.w, fmaf(2.0f, v[i].x[c + 3], -wt.x[c + 3]), acc);
-                                }
-                            }
+                auto emit = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq) {
+                    if (EMIT == EMIT_ROWS) {
+                        const float e0 = __uint_as_float(rec.x);
+                        if (on) {
+                            float* o = out + (size_t)rec.z * C4;
                             #pragma unroll
-                            for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
-                            if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
+                            for (int c = 0; c < CPL; c += 4)
+                                red_add4(o + c,
+                                         fmaf(e0, Pq.x[c],     -2.0f * Kq.x[c]),
+                                         fmaf(e0, Pq.x[c + 1], -2.0f * Kq.x[c + 1]),
+                                         fmaf(e0, Pq.x[c + 2], -2.0f * Kq.x[c + 2]),
+                                         fmaf(e0, Pq.x[c + 3], -2.0f * Kq.x[c + 3]));
                         }
-                        rec = nxt;
+                    } else {
+                        float acc = 0.0f;
+                        if (lane_on) {
+                            const float* gr = g + (size_t)rec.z * C4;
+                            #pragma unroll
+                            for (int c = 0; c < CPL; c += 4) {
+                                const float4 t4 = ldg4(gr + c);
+                                acc = fmaf(t4.x, fmaf(2.0f, Pq.x[c],     -wt.x[c]),     acc);
+                                acc = fmaf(t4.y, fmaf(2.0f, Pq.x[c + 1], -wt.x[c + 1]), acc);
+                                acc = fmaf(t4.z, fmaf(2.0f, Pq.x[c + 2], -wt.x[c + 2]), acc);
+                                acc = fmaf(t4.w, fmaf(2.0f, Pq.x[c + 3], -wt.x[c + 3]), acc);
+                            }
+                        }
+                        #pragma unroll
+                        for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
+                        if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
+                    }
+                };
+                if (cnt < (uint32_t)LPS) {
+                    uint32_t qa  = f.qs_s + cur * LPS * 16;
+                    uint4    rec = lds128u(qa);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) {
+                        while (rec.w == (uint32_t)(j0 + i)) {
+                            qa += 16;
+                            const uint4 nxt = lds128u(qa);
+                            emit(rec, v[i], kb[WITH_K ? i : 0]);
+                            rec = nxt;
+                        }
+                    }
+                } else {
+                    const uint4* yp  = f.yrec + m_lo;
+                    uint32_t     n   = 0;
+                    uint4        rec = __ldg(yp);
+                    #pragma unroll
+                    for (int i = 0; i < KB; i++) {
+                        while (n < cnt && rec.w == (uint32_t)(j0 + i)) {
+                            ++n;
+                            const uint4 nxt = __ldg(yp + n);
+                            emit(rec, v[i], kb[WITH_K ? i : 0]);
+                            rec = nxt;
+                        }
                     }
                 }
                 cur = ring_next(cur);

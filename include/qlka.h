@@ -12,7 +12,8 @@
  *
  * Limits shared by all entry points (those of the reference's check_qkv,
  * Weighted_Abs_Sum/csrc/binding.cpp:69-84 and Weighted_Laplace_Sum/csrc/binding.cpp:66-79):
- * P, D, N, M > 0, 1 <= C <= 128, N, M <= 131072, P * D * max(N, M) <= INT32_MAX.
+ * P, D, N, M > 0, 1 <= C <= 128, P * D * max(N, M) <= INT32_MAX; N, M <= 262144 here (the reference
+ * stops at 131072).
  */
 #ifndef QLKA_H
 #define QLKA_H
@@ -30,7 +31,7 @@ enum qlka_status {
     QLKA_OK = 0,
     QLKA_ERR_BAD_SHAPE = 1,        /* a size is <= 0 */
     QLKA_ERR_C_RANGE = 2,          /* C outside [1, 128] */
-    QLKA_ERR_LENGTH = 3,           /* N or M above 131072 */
+    QLKA_ERR_LENGTH = 3,           /* N or M above 262144 */
     QLKA_ERR_INT32 = 4,            /* P * D * max(N, M) does not fit int32 */
     QLKA_ERR_PATH = 5,             /* path not in {-1, 0, 1} */
     QLKA_ERR_FUSED_UNAVAILABLE = 6,/* path == 1 pinned but max(N, M) > 4096 */

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libqlka.so")
-SOURCES = ["qlka_api.cu", "sort_rank.cu", "walk_laplace.cu", "walk_prefix.cu", "aux_kernels.cu"]
+SOURCES = ["qlka_api.cu", "sort_rank.cu", "sort_rank_large.cu", "walk_laplace.cu", "walk_prefix.cu", "aux_kernels.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
          "-Xcompiler", "-fPIC", "--threads", "4"]

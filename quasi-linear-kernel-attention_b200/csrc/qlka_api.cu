@@ -8,6 +8,8 @@
 
 namespace qlka {
 cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
+cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_t stream);
+size_t      sort_rank_large_scratch_bytes(int nseg, int N, int M);
 cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream);
 cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
 int         walk_lanes_per_stream(int C4);
@@ -27,6 +29,7 @@ namespace {
 thread_local int g_last_cuda = 0;
 
 constexpr int SMALL_MAX = 16384;     // longest segment the shared-memory sort handles
+constexpr int LENGTH_MAX = 262144;   // the reference stops at 131072 (binding.cpp:78); the global-memory sort goes on
 constexpr int EMIT_ROWS = 0, EMIT_DOT = 1;
 
 #define CU(expr)                                                   \
@@ -38,10 +41,9 @@ constexpr int EMIT_ROWS = 0, EMIT_DOT = 1;
 int check_dims(int P, int D, int N, int M, int C) {
     if (P <= 0 || D <= 0 || N <= 0 || M <= 0) return QLKA_ERR_BAD_SHAPE;
     if (C < 1 || C > 128) return QLKA_ERR_C_RANGE;
-    if (N > 131072 || M > 131072) return QLKA_ERR_LENGTH;
+    if (N > LENGTH_MAX || M > LENGTH_MAX) return QLKA_ERR_LENGTH;
     const long long mx = N > M ? N : M;
     if ((long long)P * D * mx > (long long)INT_MAX) return QLKA_ERR_INT32;
-    if (mx > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;
     return QLKA_OK;
 }
 
@@ -95,7 +97,9 @@ WalkPlan plan_walk(int nseg, int N, int C4) {
 // scratch of one sort/rank run over nseg segments of N keys and M queries
 struct Records {
     uint32_t* xperm; float* xval; uint4* yrec; uint32_t* mstart; float* su0; float* su1;
+    void* large;          // extra scratch of the global-memory sort, only when max(N, M) > SMALL_MAX
     void carve(Bump& b, int nseg, int N, int M) {
+        large = (N > SMALL_MAX || M > SMALL_MAX) ? b.take<unsigned char>(sort_rank_large_scratch_bytes(nseg, N, M)) : nullptr;
         xperm  = b.take<uint32_t>((size_t)nseg * npad(N));
         xval   = b.take<float>((size_t)nseg * xstride(N));
         yrec   = b.take<uint4>((size_t)nseg * (M + 1));
@@ -111,6 +115,12 @@ SortArgs sort_args(const Records& r, const float* x, const float* y, int nseg, i
     s.xperm = r.xperm; s.xval = r.xval; s.yrec = r.yrec; s.mstart = r.mstart; s.su0 = r.su0; s.su1 = r.su1;
     s.nseg = nseg; s.D = D; s.N = N; s.M = M; s.mode = mode; s.scal = scal;
     return s;
+}
+
+// the sort/rank stage: shared-memory kernel up to SMALL_MAX elements per segment, global-memory kernels above
+cudaError_t launch_sort_rank(const SortArgs& s, const Records& r, cudaStream_t stream) {
+    if (s.N <= SMALL_MAX && s.M <= SMALL_MAX) return launch_sort_rank_small(s, stream);
+    return launch_sort_rank_large(s, r.large, stream);
 }
 
 WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int nseg, int D, int N, int M, int C4) {
@@ -193,7 +203,7 @@ const char* qlka_status_string(int status) {
         case QLKA_OK:                    return "ok";
         case QLKA_ERR_BAD_SHAPE:         return "N, M and D must be > 0";
         case QLKA_ERR_C_RANGE:           return "C (v.size(2)) must be in [1, 128]";
-        case QLKA_ERR_LENGTH:            return "N and M must be <= 131072";
+        case QLKA_ERR_LENGTH:            return "N and M must be <= 262144 (the reference: <= 131072)";
         case QLKA_ERR_INT32:             return "P*D*max(N,M) must fit int32 (cub sort offsets)";
         case QLKA_ERR_PATH:              return "path must be -1 (auto), 0 (global) or 1 (fused)";
         case QLKA_ERR_FUSED_UNAVAILABLE: return "fused path pinned but unavailable: needs max(N,M) <= 4096 and the bucket's shared memory to fit this device";
@@ -240,7 +250,7 @@ static int laplace_forward_impl(const float* q, const float* k, const float* v,
 
     SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_LAPLACE, SCAL_UNIT);
     s.out_u = out_u;
-    CU(launch_sort_rank_small(s, stream));
+    CU(launch_sort_rank(s, ws.rec, stream));
     if (ev) CU(cudaEventRecord(ev[1], stream));
 
     WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
@@ -360,7 +370,7 @@ int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v
 
     SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_ABS, full ? SCAL_UNIT : SCAL_NONE);
     s.out_u = out_u;
-    CU(launch_sort_rank_small(s, stream));
+    CU(launch_sort_rank(s, ws.rec, stream));
 
     WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
     w.out = out;
@@ -416,7 +426,7 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
     {   // grad_q: queries q walk the key stream k; prefix of v rows contracted with g_w rows
         SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, full ? SCAL_RANK : SCAL_NONE);
         s.uq = g_u;
-        CU(launch_sort_rank_small(s, stream));
+        CU(launch_sort_rank(s, ws.rec, stream));
         WalkPlan plan = plan_walk(nseg, N, C4);
         WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
         w.g = grows; w.wtotal = vsum; w.out_s = grad_q;
@@ -425,7 +435,7 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
     {   // roles swapped: queries k walk the stream q whose rows are g_w
         SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_ABS, full ? SCAL_PREFIX : SCAL_NONE);
         s.us = g_u; s.us_total = gu_total;
-        CU(launch_sort_rank_small(s, stream));
+        CU(launch_sort_rank(s, ws.rec, stream));
         WalkPlan plan = plan_walk(nseg, M, C4);
         // grad_k: prefix of g_w rows contracted with v rows (+ the g_u prefix term carried in e1)
         WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
@@ -470,7 +480,7 @@ int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v
     CU(launch_rowstat(vrows, nullptr, vsum, nullptr, nullptr, P, N, C4, stream));
 
     SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, SCAL_NONE);
-    CU(launch_sort_rank_small(s, stream));
+    CU(launch_sort_rank(s, ws.rec, stream));
     WalkPlan plan = plan_walk(nseg, N, C4);
     WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
     w.g = grows; w.wtotal = vsum; w.out_s = out; w.sign = -1.0f;
@@ -483,7 +493,8 @@ int qlka_sort_rank_workspace_bytes(int P, int D, int N, int M, size_t* bytes) {
     if (!bytes) return QLKA_ERR_NULL;
     int st = check_dims(P, D, N, M, 1);
     if (st) return st;
-    *bytes = sizeof(float) * 2 * (size_t)P * D * (N + 1) + 512;
+    *bytes = sizeof(float) * 2 * (size_t)P * D * (N + 1) + 1024
+           + ((N > SMALL_MAX || M > SMALL_MAX) ? sort_rank_large_scratch_bytes(P * D, N, M) : 0);
     return QLKA_OK;
 }
 
@@ -504,8 +515,9 @@ int qlka_sort_rank_records(const float* x, const float* y,
     r.xperm = xperm; r.xval = xval; r.yrec = reinterpret_cast<uint4*>(yrec); r.mstart = mstart;
     r.su0 = b.take<float>((size_t)P * D * (N + 1));
     r.su1 = b.take<float>((size_t)P * D * (N + 1));
+    r.large = (N > SMALL_MAX || M > SMALL_MAX) ? b.take<unsigned char>(sort_rank_large_scratch_bytes(P * D, N, M)) : nullptr;
     SortArgs s = sort_args(r, x, y, P * D, D, N, M, mode, SCAL_NONE);
-    CU(launch_sort_rank_small(s, reinterpret_cast<cudaStream_t>(stream_)));
+    CU(launch_sort_rank(s, r, reinterpret_cast<cudaStream_t>(stream_)));
     return QLKA_OK;
 }
 

@@ -78,6 +78,13 @@ __device__ __forceinline__ float key2f(uint32_t u) {
     return __uint_as_float((u & 0x80000000u) ? (u & 0x7fffffffu) : ~u);
 }
 
+// exp(-gap) for gap >= 0, correctly rounded near 1: the step decays of dense keys are all within a few
+// thousand ulps of 1 and thousands of them multiply into every prefix state, so their rounding error is
+// what limits the accuracy of the Laplace recurrences; expf alone is off by up to 2 ulp there
+__device__ __forceinline__ float decay_of(const float gap) {
+    return gap < 0.5f ? 1.0f + expm1f(-gap) : expf(-gap);
+}
+
 // 16-byte vector reduction into global memory (no return value)
 __device__ __forceinline__ void red_add4(float* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"

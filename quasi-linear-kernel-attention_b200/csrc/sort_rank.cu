@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
             #pragma unroll
             for (int k = 0; k <= R; k++) {
                 const int j = i0 + k;
-                dk[k] = (k <= cntk && j > 0 && j < N) ? expf(-(xs[skew(j)] - xs[skew(j - 1)])) : 0.0f;
+                dk[k] = (k <= cntk && j > 0 && j < N) ? decay_of(xs[skew(j)] - xs[skew(j - 1)]) : 0.0f;
             }
             float bx[R];
             #pragma unroll

@@ -45,9 +45,9 @@ def test_dimension_checks_follow_the_reference(lib):
     assert f(2, 4, 100, 100, 8, ctypes.byref(n)) == 0 and n.value > 0
     assert f(0, 4, 100, 100, 8, ctypes.byref(n)) == 1           # sizes must be > 0
     assert f(2, 4, 100, 100, 129, ctypes.byref(n)) == 2         # C in [1, 128]
-    assert f(2, 4, 131073, 100, 8, ctypes.byref(n)) == 3        # N, M <= 131072
+    assert f(2, 4, 262145, 100, 8, ctypes.byref(n)) == 3        # N, M <= 262144 (the reference: 131072)
     assert f(4096, 64, 16384, 16384, 8, ctypes.byref(n)) == 4   # P*D*max(N,M) must fit int32
-    assert b"131072" in lib.qlka_status_string(3)
+    assert b"262144" in lib.qlka_status_string(3)
     assert b"int32" in lib.qlka_status_string(4)
     # forward calls refuse before any launch: bad path, pinned fused path, null pointers, short workspace
     fwd = lib.qlka_weighted_abs_sum_forward

@@ -134,6 +134,71 @@ def laplace_forward_noalloc(q, k, v, out_w=None, out_u=None):
     return out_w, out_u
 
 
+class HostPipeline:
+    """weighted Laplace sum for inputs and outputs in (pinned) host memory.
+
+    The heads (dim 0 = P) are cut into chunks that flow through three CUDA streams - host-to-device
+    copies, the operator, device-to-host copies - with two sets of device buffers, so that the PCIe
+    transfers of one chunk overlap the kernels of the previous one and the read-back of the one
+    before. Device buffers and the workspace are allocated once, at construction.
+    """
+
+    def __init__(self, P, D, N, M, C, chunk, device=None):
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.dims = (P, D, N, M, C)
+        self.chunk = max(1, min(chunk, P))
+        L = lib()
+        with torch.cuda.device(self.device):
+            n = _sz(0)
+            st = L.qlka_laplace_forward_workspace_bytes(self.chunk, D, N, M, C, ctypes.byref(n))
+            if st:
+                _raise(st)
+            self.ws_bytes = int(n.value)
+            f32 = dict(dtype=torch.float32, device=self.device)
+            self.sets = [dict(q=torch.empty(self.chunk, D, M, **f32), k=torch.empty(self.chunk, D, N, **f32),
+                              v=torch.empty(self.chunk, N, C, **f32), ow=torch.empty(self.chunk, M, C, **f32),
+                              ou=torch.empty(self.chunk, M, **f32),
+                              ws=torch.empty(max(self.ws_bytes, 256), dtype=torch.uint8, device=self.device),
+                              loaded=torch.cuda.Event(), computed=torch.cuda.Event(), drained=torch.cuda.Event())
+                         for _ in range(2)]
+            self.s_in, self.s_run, self.s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+
+    def __call__(self, q_h, k_h, v_h, out_w_h, out_u_h):
+        """Enqueue one pass over all heads; returns after everything has been enqueued. The caller
+        synchronises (e.g. torch.cuda.synchronize()) before reading out_w_h / out_u_h."""
+        P, D, N, M, C = self.dims
+        L = lib()
+        cur = torch.cuda.current_stream(self.device)
+        for s in (self.s_in, self.s_run, self.s_out):
+            s.wait_stream(cur)
+        with torch.cuda.device(self.device):
+            for i, lo in enumerate(range(0, P, self.chunk)):
+                hi, b = min(P, lo + self.chunk), self.sets[i % 2]
+                n = hi - lo
+                with torch.cuda.stream(self.s_in):
+                    self.s_in.wait_event(b["computed"])          # the previous user of this buffer set has consumed its inputs
+                    b["q"][:n].copy_(q_h[lo:hi], non_blocking=True)
+                    b["k"][:n].copy_(k_h[lo:hi], non_blocking=True)
+                    b["v"][:n].copy_(v_h[lo:hi], non_blocking=True)
+                    b["loaded"].record(self.s_in)
+                with torch.cuda.stream(self.s_run):
+                    self.s_run.wait_event(b["loaded"])
+                    self.s_run.wait_event(b["drained"])          # ... and its outputs have left the device
+                    st = L.qlka_weighted_laplace_sum_forward(b["q"].data_ptr(), b["k"].data_ptr(), b["v"].data_ptr(),
+                                                             b["ow"].data_ptr(), b["ou"].data_ptr(), b["ws"].data_ptr(),
+                                                             self.ws_bytes, n, D, N, M, C, self.s_run.cuda_stream)
+                    if st:
+                        _raise(st)
+                    b["computed"].record(self.s_run)
+                with torch.cuda.stream(self.s_out):
+                    self.s_out.wait_event(b["computed"])
+                    out_w_h[lo:hi].copy_(b["ow"][:n], non_blocking=True)
+                    out_u_h[lo:hi].copy_(b["ou"][:n], non_blocking=True)
+                    b["drained"].record(self.s_out)
+        for s in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(s)
+
+
 def laplace_stage_times(q, k, v, reps=5):
     """Diagnostic: median device time (ms) of the sort/rank kernel and of the walk kernel."""
     P, D, N, M, C = dims = check_qkv(q, k, v)

@@ -102,3 +102,18 @@ def test_argument_errors():
         weighted_laplace_sum(q, k, v[:, :8])
     with pytest.raises(RuntimeError, match=r"\[1, 128\]"):
         weighted_laplace_sum(q, k, torch.zeros(1, 16, 129, device="cuda"))
+
+
+def test_host_pipeline_matches_device_call():
+    """Pinned host buffers in and out, heads streamed in chunks (ragged last chunk)."""
+    import qlka_native
+    P, D, N, M, C = 7, 4, 1200, 900, 32
+    q, k, v = make_inputs(P, D, N, M, C, seed=77, scale=2.0, device="cpu")
+    q_h, k_h, v_h = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    out_w_h, out_u_h = torch.empty(P, M, C).pin_memory(), torch.empty(P, M).pin_memory()
+    pipe = qlka_native.HostPipeline(P, D, N, M, C, chunk=3)
+    for _ in range(2):
+        pipe(q_h, k_h, v_h, out_w_h, out_u_h)
+        torch.cuda.synchronize()
+        ref_w, ref_u = qlka_native.laplace_forward(q.cuda(), k.cuda(), v.cuda())
+        assert rel_err(out_w_h, ref_w.double()) < 1e-5 and rel_err(out_u_h, ref_u.double()) < 1e-5

@@ -30,7 +30,7 @@ thread_local int g_last_cuda = 0;
 
 constexpr int SMALL_MAX = 16384;     // longest segment the shared-memory sort handles
 constexpr int LENGTH_MAX = 262144;   // the reference stops at 131072 (binding.cpp:78); the global-memory sort goes on
-constexpr int EMIT_ROWS = 0, EMIT_DOT = 1;
+constexpr int EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2;
 
 #define CU(expr)                                                   \
     do {                                                           \
@@ -437,15 +437,12 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
         s.us = g_u; s.us_total = gu_total;
         CU(launch_sort_rank(s, ws.rec, stream));
         WalkPlan plan = plan_walk(nseg, M, C4);
-        // grad_k: prefix of g_w rows contracted with v rows (+ the g_u prefix term carried in e1)
-        WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
-        w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k;
-        CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
-        // grad_v: abs sum with keys q, weights g_w, evaluated at the keys k
+        // one walk for both: grad_v = abs sum with keys q, weights g_w, evaluated at the keys k (row reductions on
+        // top of its rank-1 initial value); grad_k = prefix of g_w rows contracted with v rows (+ the g_u term in e1)
         CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, stream));
-        WalkArgs w2 = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
-        w2.out = gv;
-        CU(launch_prefix_walk(w2, EMIT_ROWS, plan.grid, stream));
+        WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
+        w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k; w.out = gv;
+        CU(launch_prefix_walk(w, EMIT_BOTH, plan.grid, stream));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
     return QLKA_OK;

@@ -4,6 +4,7 @@
 //   EMIT_ROWS  out[p, row_m, :] += e0_m * PV - 2 * PK          (vector reductions)
 //              with e0 = 2 * query this is the walk term 2 (q PV - PK) of the abs sum
 //              (Weighted_Abs_Sum/csrc/abs_kernels.cu:9-18; abs_chunk :78-199, abs_prefix :202-405)
+//   EMIT_BOTH  both of the others from one walk (grad_v and grad_k share stream, rows and queries)
 //   EMIT_DOT   out_s[seg, row_m] = sign * ( <g[p, row_m, :], 2 PV - wtotal[p, :]> + e1_m )
 //              the signed-rank walk behind grad_q, grad_k and the public sgn op
 //              (Weighted_Abs_Sum/csrc/sgn_kernels.cu:8-15, sgn_prefix :17-192); one writer per
@@ -17,14 +18,15 @@
 
 namespace qlka {
 
-enum { EMIT_ROWS = 0, EMIT_DOT = 1 };
+enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2 };     // BOTH: one walk feeds a row reduction and a dot output
 
 template <int LPS, int CPL, int EMIT>
 __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(const WalkArgs a)
 {
     constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr int  CW      = LPS * CPL;
-    constexpr bool WITH_K  = EMIT == EMIT_ROWS;
+    constexpr bool WITH_K  = EMIT != EMIT_DOT;
+    constexpr bool DO_ROWS = EMIT != EMIT_DOT, DO_DOT = EMIT != EMIT_ROWS;
     extern __shared__ __align__(16) float4 smem[];
     float4* ring   = smem;
     uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
@@ -128,16 +130,16 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
         // emit-side constants
         Vec<CPL> wt;
         wt.zero();
-        if (EMIT == EMIT_DOT) {
+        if (DO_DOT) {
             #pragma unroll
             for (int c = 0; c < CPL; c += 4) {
                 const float4 t = ldg4(a.wtotal + (long long)p * C4 + c0l + c);
                 wt.x[c] = t.x; wt.x[c + 1] = t.y; wt.x[c + 2] = t.z; wt.x[c + 3] = t.w;
             }
         }
-        float*       out   = EMIT == EMIT_ROWS ? a.out + (long long)p * M * C4 + c0l : nullptr;
-        const float* g     = EMIT == EMIT_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
-        float*       out_s = EMIT == EMIT_DOT ? a.out_s + (long long)sg * M : nullptr;
+        float*       out   = DO_ROWS ? a.out + (long long)p * M * C4 + c0l : nullptr;
+        const float* g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
+        float*       out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
 
         // ---------------- pass 2: forward with emission
         {
@@ -170,8 +172,16 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t2, PK.x[c]); }
                     }
                 }
-                auto emit = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq) {
-                    if (EMIT == EMIT_ROWS) {
+                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record (row 0 for the sentinel)
+                    const float* gr = g + (size_t)rec.z * C4;
+                    #pragma unroll
+                    for (int c = 0; c < CPL; c += 4) {
+                        const float4 t4 = lane_on ? ldg4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        gq.x[c] = t4.x; gq.x[c + 1] = t4.y; gq.x[c + 2] = t4.z; gq.x[c + 3] = t4.w;
+                    }
+                };
+                auto emit = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq, const Vec<CPL>& gq) {
+                    if (DO_ROWS) {
                         const float e0 = __uint_as_float(rec.x);
                         if (on) {
                             float* o = out + (size_t)rec.z * C4;
@@ -183,19 +193,11 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                                          fmaf(e0, Pq.x[c + 2], -2.0f * Kq.x[c + 2]),
                                          fmaf(e0, Pq.x[c + 3], -2.0f * Kq.x[c + 3]));
                         }
-                    } else {
+                    }
+                    if (DO_DOT) {
                         float acc = 0.0f;
-                        if (lane_on) {
-                            const float* gr = g + (size_t)rec.z * C4;
-                            #pragma unroll
-                            for (int c = 0; c < CPL; c += 4) {
-                                const float4 t4 = ldg4(gr + c);
-                                acc = fmaf(t4.x, fmaf(2.0f, Pq.x[c],     -wt.x[c]),     acc);
-                                acc = fmaf(t4.y, fmaf(2.0f, Pq.x[c + 1], -wt.x[c + 1]), acc);
-                                acc = fmaf(t4.z, fmaf(2.0f, Pq.x[c + 2], -wt.x[c + 2]), acc);
-                                acc = fmaf(t4.w, fmaf(2.0f, Pq.x[c + 3], -wt.x[c + 3]), acc);
-                            }
-                        }
+                        #pragma unroll
+                        for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(2.0f, Pq.x[c], -wt.x[c]), acc);
                         #pragma unroll
                         for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
                         if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
@@ -204,12 +206,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                 if (cnt < (uint32_t)LPS) {
                     uint32_t qa  = f.qs_s + cur * LPS * 16;
                     uint4    rec = lds128u(qa);
+                    Vec<CPL> gq, gn;                  // emit-side rows are fetched one record ahead
+                    gn.zero();
+                    if (DO_DOT) load_g(rec, gn);
                     #pragma unroll
                     for (int i = 0; i < KB; i++) {
                         while (rec.w == (uint32_t)(j0 + i)) {
                             qa += 16;
                             const uint4 nxt = lds128u(qa);
-                            emit(rec, v[i], kb[WITH_K ? i : 0]);
+                            gq = gn;
+                            if (DO_DOT) load_g(nxt, gn);
+                            emit(rec, v[i], kb[WITH_K ? i : 0], gq);
                             rec = nxt;
                         }
                     }
@@ -222,7 +229,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
                         while (n < cnt && rec.w == (uint32_t)(j0 + i)) {
                             ++n;
                             const uint4 nxt = __ldg(yp + n);
-                            emit(rec, v[i], kb[WITH_K ? i : 0]);
+                            Vec<CPL> gq;
+                            gq.zero();
+                            if (DO_DOT) load_g(rec, gq);
+                            emit(rec, v[i], kb[WITH_K ? i : 0], gq);
                             rec = nxt;
                         }
                     }
@@ -249,10 +259,14 @@ cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream
         if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_ROWS>(a, grid, stream);
         if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_ROWS>(a, grid, stream);
         if (a.C4 <= 128) return launch_pw<16, 8, EMIT_ROWS>(a, grid, stream);
-    } else {
+    } else if (emit == EMIT_DOT) {
         if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_DOT>(a, grid, stream);
         if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_DOT>(a, grid, stream);
         if (a.C4 <= 128) return launch_pw<16, 8, EMIT_DOT>(a, grid, stream);
+    } else {
+        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_BOTH>(a, grid, stream);
+        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_BOTH>(a, grid, stream);
+        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_BOTH>(a, grid, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -5,6 +5,7 @@
 #include "qlka_common.cuh"
 
 #include <climits>
+#include <cstdlib>
 
 namespace qlka {
 cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
@@ -77,7 +78,8 @@ struct WalkPlan { int sps, segs, nitems, grid; };
 WalkPlan plan_walk(int nseg, int N, int C4) {
     const int lps      = walk_lanes_per_stream(C4);
     const int streams  = 256 / lps;
-    const int per_sm   = C4 <= 64 ? 2 : 1;
+    int per_sm = C4 <= 64 ? 2 : 1;              // resident walk CTAs per SM (registers and shared memory)
+    if (const char* e = std::getenv("QLKA_WALK_CTAS_PER_SM")) { const int v = std::atoi(e); if (v >= 1 && v <= 8) per_sm = v; }   // tuning aid
     const int grid_cap = sm_count() * per_sm;
     const int nbk      = nblocks(N);
     int sps_max = 1;

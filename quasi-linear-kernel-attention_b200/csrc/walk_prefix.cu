@@ -21,7 +21,7 @@ namespace qlka {
 enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2 };     // BOTH: one walk feeds a row reduction and a dot output
 
 template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(const WalkArgs a)
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS : 1)) prefix_walk(const WalkArgs a)
 {
     constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr int  CW      = LPS * CPL;
@@ -50,6 +50,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
     f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = WITH_K;
 
+    // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
         const int  seg    = item * SEGS + sl;
         const bool seg_on = seg < a.nseg;
@@ -72,16 +73,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
         if (SPS > 1) {
             // ---------------- pass 1: stream sums
             f.with_q = false;
-            if (nblk > 0) { f.prefetch_index(b0); f.issue(0, b0); } else cp_async_commit();
-            if (nblk > 1) { f.prefetch_index(b0 + 1); f.issue(1, b0 + 1); } else cp_async_commit();
-            if (nblk > 2) f.prefetch_index(b0 + 2);
+            f.prologue(b0, 1, nblk);
             int cur = 0;
             for (int t = 0; t < nblk; t++) {
                 const int b = b0 + t, j0 = b * KB;
                 __syncwarp(gmask);
-                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
-                if (t + 3 < nblk) f.prefetch_index(b + 3);
-                cp_async_wait<RING_DEPTH - 1>();
+                f.step(t, cur, b0, 1, nblk);
                 float kv[KB + 1];
                 if (WITH_K) {
                     __syncwarp(gmask);
@@ -144,16 +141,12 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 2 : 1)) prefix_walk(
         // ---------------- pass 2: forward with emission
         {
             f.with_q = true;
-            if (nblk > 0) { f.prefetch_index(b0); f.issue(0, b0); } else cp_async_commit();
-            if (nblk > 1) { f.prefetch_index(b0 + 1); f.issue(1, b0 + 1); } else cp_async_commit();
-            if (nblk > 2) f.prefetch_index(b0 + 2);
+            f.prologue(b0, 1, nblk);
             int cur = 0;
             for (int t = 0; t < nblk; t++) {
                 const int b = b0 + t, j0 = b * KB;
                 __syncwarp(gmask);
-                if (t + 2 < nblk) f.issue(ring_ahead2(cur), b + 2); else cp_async_commit();
-                if (t + 3 < nblk) f.prefetch_index(b + 3);
-                cp_async_wait<RING_DEPTH - 1>();
+                f.step(t, cur, b0, 1, nblk);
                 __syncwarp(gmask);
                 float kv[KB + 1];
                 uint32_t m_lo, m_hi;

@@ -2,7 +2,7 @@
 //
 // Every thread owns a private ring of RING_DEPTH slots in shared memory; a slot holds the
 // thread's CPL-channel slice of the KB rows of one key block. Rows are fetched with cp.async
-// (global -> shared, no registers, L2 only) two blocks ahead of their use, one commit group
+// (global -> shared, no registers, L2 only) one block ahead of their use, one commit group
 // per block, so the L2 latency of the row gather is hidden without extra warps. A thread only
 // ever reads the rows it copied itself, so cp.async.wait_group is all the rows need.
 //
@@ -18,7 +18,14 @@
 namespace qlka {
 
 constexpr int WALK_THREADS = 256;
-constexpr int RING_DEPTH   = 3;      // blocks in flight: the one in use and two prefetched
+#ifndef QLKA_RING_DEPTH
+#define QLKA_RING_DEPTH 2
+#endif
+#ifndef QLKA_WALK_MIN_CTAS
+#define QLKA_WALK_MIN_CTAS 2
+#endif
+constexpr int RING_DEPTH   = QLKA_RING_DEPTH;   // blocks in flight: the one in use and RING_DEPTH - 1 prefetched
+constexpr int RING_AHEAD   = RING_DEPTH - 1;
 constexpr int SX_STRIDE    = 12;     // floats per staged scalar slot: 8 decays / keys, the next one, pad, m_lo, m_hi
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -131,6 +138,23 @@ struct Feeder {
         cp_async_commit();
     }
 
+    // Blocks are visited in steps t = 0 .. nblk-1, block of step t = bfirst + dir * t, slot of step t = t mod RING_DEPTH.
+    // prologue: start the first RING_AHEAD blocks; step: start block t + RING_AHEAD, then wait for block t.
+    __device__ __forceinline__ void prologue(const int bfirst, const int dir, const int nblk) {
+        #pragma unroll
+        for (int s = 0; s < RING_AHEAD; s++) {
+            if (s < nblk) { prefetch_index(bfirst + dir * s); issue(s, bfirst + dir * s); }
+            else cp_async_commit();
+        }
+        if (RING_AHEAD < nblk) prefetch_index(bfirst + dir * RING_AHEAD);
+    }
+    __device__ __forceinline__ void step(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
+        if (t + RING_AHEAD < nblk) issue(cur == 0 ? RING_DEPTH - 1 : cur - 1, bfirst + dir * (t + RING_AHEAD));
+        else cp_async_commit();
+        if (t + RING_AHEAD + 1 < nblk) prefetch_index(bfirst + dir * (t + RING_AHEAD + 1));
+        cp_async_wait<RING_AHEAD>();
+    }
+
     // this thread's slice of the block's rows from `slot`; rows at positions >= N read as zero
     __device__ __forceinline__ void read_rows(const int slot, const int j0, Vec<CPL> (&v)[KB]) const {
         const uint32_t src = ring_s + slot * ring_slot_bytes<CPL>();
@@ -160,6 +184,5 @@ struct Feeder {
 };
 
 __device__ __forceinline__ int ring_next(const int cur) { return cur == RING_DEPTH - 1 ? 0 : cur + 1; }
-__device__ __forceinline__ int ring_ahead2(const int cur) { return cur >= RING_DEPTH - 2 ? cur + 2 - RING_DEPTH : cur + 2; }
 
 }  // namespace qlka

@@ -183,10 +183,11 @@ __device__ __forceinline__ void block_exclusive_sum(uint32_t* __restrict__ h, co
     for (int i = i0; i < i1; i++) { uint32_t c = h[i]; h[i] = pre; pre += c; }
 }
 
-// The sorted keys sit in shared memory with one word of padding after every 32: a binary search
+// The sorted keys sit in shared memory with a word of padding after every 32 and another after every
+// 1024, so that probe positions that differ by any power of two fall into different banks: a binary search
 // over a power-of-two array otherwise probes addresses that are multiples of a large power of two,
 // i.e. one bank, in its first ten steps.
-__device__ __forceinline__ int skew(const int i) { return i + (i >> 5); }
+__device__ __forceinline__ int skew(const int i) { return i + (i >> 5) + (i >> 10); }
 
 __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const int n, const float x) {
     int lo = 0, hi = n;
@@ -194,35 +195,13 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
     return lo;
 }
 
-// One query's record into its staging slot, plus its share of the unit column or its scalar term.
-__device__ __noinline__ void make_record(const SortArgs& a, const float* __restrict__ xs, const float* __restrict__ su0s,
-                                         const float* __restrict__ su0, const float* __restrict__ su1,
-                                         const float* __restrict__ ysrc, uint4* __restrict__ slot,
-                                         const int p, const int m, const int r)
-{
-    const int   N = a.N, M = a.M;
-    const float y = ysrc[m];
-    float e0 = 0.0f, e1 = 0.0f;
-    if (a.mode == MODE_LAPLACE) {
-        e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
-        e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
-        if (a.scal == SCAL_UNIT)
-            atomicAdd(a.out_u + (long long)p * M + m, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
-    } else {
-        if (a.mode == MODE_ABS) e0 = 2.0f * y;
-        if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
-        else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
-        else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
-    }
-    *slot = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
-}
-
 // ------------------------------------------------------------------ the kernel
 // Phases: (1) radix sort of the keys; (2) per-key decays and the scalar scans, each thread on a
 // contiguous run of keys with the decays in registers; (3) the queries are not sorted by value:
 // each is ranked against the sorted keys by binary search and the records are ordered by rank
 // with a counting sort (shared-memory histogram over the N + 1 ranks, exclusive scan, atomic
-// cursor), which also yields mstart for free. Queries of equal rank come out in arbitrary order,
+// cursor), which also yields mstart for free; the records are then built in position order. Queries of
+// equal rank come out in arbitrary order,
 // which the walk does not care about.
 template <int THREADS, int E>
 __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
@@ -232,7 +211,7 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
     extern __shared__ __align__(16) unsigned char smem_raw[];
     uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);        // sort buffer, later the rank histogram (CAP + 1 + pad)
     float*    xs   = reinterpret_cast<float*>(skey + CAP + 32);    // sorted keys
-    uint32_t* base = reinterpret_cast<uint32_t*>(xs + CAP + CAP / 32);
+    uint32_t* base = reinterpret_cast<uint32_t*>(xs + CAP + CAP / 32 + 32);
     uint32_t* wsum = base + 256;
     float*    wa   = reinterpret_cast<float*>(wsum + 32);
     float*    wb   = wa + 32;
@@ -369,22 +348,32 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
     for (int s = 0; s < E; s++)
         if (tid + s * THREADS < M) rp[s] |= atomicAdd(&hist[rp[s]], 1u) << 16;       // final position of the record
     __syncthreads();
-    // the histogram is spent: its memory stages the records, a chunk of positions at a time, so that
-    // they reach global memory as full coalesced lines
-    uint4* stage4 = reinterpret_cast<uint4*>(skey);
-    constexpr int CHUNK = CAP / 4;                    // records per round (16 bytes each: CAP * 4 bytes of staging)
-    for (int c0 = 0; c0 < M; c0 += CHUNK) {
-        #pragma unroll
-        for (int s = 0; s < E; s++) {
-            const int      m   = tid + s * THREADS;
-            const uint32_t pos = rp[s] >> 16;
-            if (m < M && pos >= (uint32_t)c0 && pos < (uint32_t)(c0 + CHUNK))
-                make_record(a, xs, su0s, su0, su1, ysrc, stage4 + (pos - c0), p, m, (int)(rp[s] & 0xffffu));
+    // the histogram is spent: its memory now maps every record position to its query (index | rank << 16),
+    // so that the records can be built and written in position order, as full coalesced lines
+    uint32_t* who = skey;
+    #pragma unroll
+    for (int s = 0; s < E; s++) {
+        const int m = tid + s * THREADS;
+        if (m < M) who[rp[s] >> 16] = (uint32_t)m | (rp[s] << 16);
+    }
+    __syncthreads();
+    for (int pos = tid; pos < M; pos += THREADS) {
+        const uint32_t w = who[pos];
+        const int      m = (int)(w & 0xffffu), r = (int)(w >> 16);
+        const float    y = ysrc[m];
+        float e0 = 0.0f, e1 = 0.0f;
+        if (a.mode == MODE_LAPLACE) {
+            e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
+            e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
+            if (a.scal == SCAL_UNIT)
+                atomicAdd(a.out_u + (long long)p * M + m, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+        } else {
+            if (a.mode == MODE_ABS) e0 = 2.0f * y;
+            if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
+            else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
+            else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
         }
-        __syncthreads();
-        const int nrec = min(CHUNK, M - c0);
-        for (int i = tid; i < nrec; i += THREADS) yrec[c0 + i] = stage4[i];
-        __syncthreads();
+        yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
     PHASE_STAMP(6);
@@ -400,7 +389,7 @@ template <int THREADS, int E>
 static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
-    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
+    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
     auto kern = sort_rank_small<THREADS, E>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -42,25 +42,37 @@ __device__ __forceinline__ void block_radix_sort(
         const int shift = 8 * pass;
         for (int i = tid; i < W * 256; i += THREADS) cnt[i] = 0;
         __syncthreads();
+        if (pass == 1) PHASE_STAMP(8);
 
         uint32_t rk[E];
         #pragma unroll
-        for (int s = 0; s < E; s++) {
-            const uint32_t d      = (key[s] >> shift) & 255u;
-            uint32_t       peers  = FULL;                  // lanes holding the same digit: eight ballots
-            #pragma unroll                                 // (match.any has the same result but a far lower rate)
-            for (int bit = 0; bit < 8; bit++) {
-                const uint32_t vote = __ballot_sync(FULL, (d >> bit) & 1u);
-                peers &= ((d >> bit) & 1u) ? vote : ~vote;
+        for (int s0 = 0; s0 < E; s0 += 4) {
+            // the peer masks of four steps first (independent votes), then their counter updates in order
+            uint32_t peers[4];
+            #pragma unroll
+            for (int t = 0; t < 4; t++) peers[t] = FULL;
+            #pragma unroll                                 // lanes holding the same digit: eight ballots per step
+            for (int bit = 0; bit < 8; bit++) {            // (match.any has the same result but a far lower rate)
+                #pragma unroll
+                for (int t = 0; t < 4; t++) {
+                    const uint32_t b    = (key[s0 + t] >> (shift + bit)) & 1u;
+                    const uint32_t vote = __ballot_sync(FULL, b);
+                    peers[t] &= b ? vote : ~vote;
+                }
             }
-            const int      leader = __ffs(peers) - 1;
-            uint32_t       old    = 0;
-            if (lane == leader) { old = mycnt[d]; mycnt[d] = old + __popc(peers); }
-            old   = __shfl_sync(FULL, old, leader);
-            rk[s] = old + __popc(peers & lt);
-            __syncwarp();
+            #pragma unroll
+            for (int t = 0; t < 4; t++) {
+                const uint32_t d      = (key[s0 + t] >> shift) & 255u;
+                const int      leader = __ffs(peers[t]) - 1;
+                uint32_t       old    = 0;
+                if (lane == leader) { old = mycnt[d]; mycnt[d] = old + __popc(peers[t]); }
+                old        = __shfl_sync(FULL, old, leader);
+                rk[s0 + t] = old + __popc(peers[t] & lt);
+                __syncwarp();
+            }
         }
         __syncthreads();
+        if (pass == 1) PHASE_STAMP(9);
 
         // per digit: exclusive scan over warps, then exclusive scan of the digit totals
         uint32_t tot = 0, incl = 0;
@@ -84,6 +96,7 @@ __device__ __forceinline__ void block_radix_sort(
             base[tid] = pre + incl - tot;
         }
         __syncthreads();
+        if (pass == 1) PHASE_STAMP(10);
 
         #pragma unroll
         for (int s = 0; s < E; s++) {
@@ -93,6 +106,7 @@ __device__ __forceinline__ void block_radix_sort(
             sidx[dst] = (uint16_t)idx[s];
         }
         __syncthreads();
+        if (pass == 1) PHASE_STAMP(11);
         if (pass < 3) {
             #pragma unroll
             for (int s = 0; s < E; s++) {
@@ -101,6 +115,7 @@ __device__ __forceinline__ void block_radix_sort(
                 idx[s] = sidx[pos];
             }
         }
+        if (pass == 1) PHASE_STAMP(12);
     }
 }
 
@@ -357,6 +372,7 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
         if (m < M) who[rp[s] >> 16] = (uint32_t)m | (rp[s] << 16);
     }
     __syncthreads();
+    #pragma unroll 4
     for (int pos = tid; pos < M; pos += THREADS) {
         const uint32_t w = who[pos];
         const int      m = (int)(w & 0xffffu), r = (int)(w >> 16);

@@ -11,14 +11,6 @@
 
 namespace qlka {
 
-// Optional per-phase cycle stamps of CTA 0 (development aid; compiled out unless QLKA_PHASE_TIMING is defined).
-#ifdef QLKA_PHASE_TIMING
-__device__ long long g_phase_clock[16];
-#define PHASE_STAMP(i) do { __syncthreads(); if (blockIdx.x == 0 && threadIdx.x == 0) g_phase_clock[i] = clock64(); } while (0)
-#else
-#define PHASE_STAMP(i) do {} while (0)
-#endif
-
 // ------------------------------------------------------------------ block radix sort
 // Elements are held in registers, E per thread, in warp-blocked order: the element at
 // array position warp*32*E + s*32 + lane sits in slot s of that lane. One pass ranks each
@@ -42,7 +34,6 @@ __device__ __forceinline__ void block_radix_sort(
         const int shift = 8 * pass;
         for (int i = tid; i < W * 256; i += THREADS) cnt[i] = 0;
         __syncthreads();
-        if (pass == 1) PHASE_STAMP(8);
 
         uint32_t rk[E];
         #pragma unroll
@@ -72,7 +63,6 @@ __device__ __forceinline__ void block_radix_sort(
             }
         }
         __syncthreads();
-        if (pass == 1) PHASE_STAMP(9);
 
         // per digit: exclusive scan over warps, then exclusive scan of the digit totals
         uint32_t tot = 0, incl = 0;
@@ -96,7 +86,6 @@ __device__ __forceinline__ void block_radix_sort(
             base[tid] = pre + incl - tot;
         }
         __syncthreads();
-        if (pass == 1) PHASE_STAMP(10);
 
         #pragma unroll
         for (int s = 0; s < E; s++) {
@@ -106,7 +95,6 @@ __device__ __forceinline__ void block_radix_sort(
             sidx[dst] = (uint16_t)idx[s];
         }
         __syncthreads();
-        if (pass == 1) PHASE_STAMP(11);
         if (pass < 3) {
             #pragma unroll
             for (int s = 0; s < E; s++) {
@@ -115,7 +103,6 @@ __device__ __forceinline__ void block_radix_sort(
                 idx[s] = sidx[pos];
             }
         }
-        if (pass == 1) PHASE_STAMP(12);
     }
 }
 
@@ -246,22 +233,17 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
     uint32_t* mstart = a.mstart + (long long)seg * mstride(N);
     float*    su0    = a.su0 ? a.su0 + (long long)seg * (N + 1) : nullptr;
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
-
-    PHASE_STAMP(0);
     // ---- (1) keys
     {
         uint32_t key[E], idx[E];
         load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
         block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
     }
-    PHASE_STAMP(1);
     for (int j = tid; j < NP; j += THREADS) {
         if (j < N) xs[skew(j)] = key2f(skey[j]);
         xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     }
     __syncthreads();
-
-    PHASE_STAMP(2);
     // ---- (2) per-key scalars; my run of keys is [i0, i0 + cntk). The run length is odd so that the
     // strided shared-memory accesses below are bank-conflict free; results leave through a staging
     // buffer (the idle sort buffer) so that the global stores are coalesced.
@@ -319,45 +301,41 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
         }
     }
     __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
-
-    PHASE_STAMP(3);
     // ---- (3) queries: rank, counting sort by rank, records
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();
     const float* ysrc = a.y + (long long)seg * M;
     uint32_t rp[E];                                   // rank, later rank | position << 16 (both <= 16384)
-    // branch-free binary search, four queries in flight per thread
+    // branch-free binary search, QI queries in flight per thread (the probes are latency bound)
+    constexpr int QI = E >= 8 ? 8 : 4;
     #pragma unroll
-    for (int s0 = 0; s0 < E; s0 += 4) {
-        int   pos4[4];
-        float y4[4];
+    for (int s0 = 0; s0 < E; s0 += QI) {
+        int   posq[QI];
+        float yq[QI];
         #pragma unroll
-        for (int t = 0; t < 4; t++) {
+        for (int t = 0; t < QI; t++) {
             const int m = tid + (s0 + t) * THREADS;
-            y4[t]   = m < M ? ysrc[m] : 0.0f;
-            pos4[t] = 0;
+            yq[t]   = m < M ? ysrc[m] : 0.0f;
+            posq[t] = 0;
         }
         #pragma unroll
         for (int step = CAP; step >= 1; step >>= 1) {
             #pragma unroll
-            for (int t = 0; t < 4; t++) {
-                const int probe = pos4[t] + step;
-                if (probe <= N && xs[skew(probe - 1)] < y4[t]) pos4[t] = probe;
+            for (int t = 0; t < QI; t++) {
+                const int probe = posq[t] + step;
+                if (probe <= N && xs[skew(probe - 1)] < yq[t]) posq[t] = probe;
             }
         }
         #pragma unroll
-        for (int t = 0; t < 4; t++) rp[s0 + t] = (uint32_t)pos4[t];     // number of keys strictly below the query
+        for (int t = 0; t < QI; t++) rp[s0 + t] = (uint32_t)posq[t];     // number of keys strictly below the query
     }
-    PHASE_STAMP(7);
     #pragma unroll
     for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rp[s]], 1u);
     __syncthreads();
-    PHASE_STAMP(4);
     block_exclusive_sum<THREADS, E>(hist, N + 1, wsum);
     __syncthreads();
     for (int b = tid; b <= NBK; b += THREADS) mstart[b] = b == NBK ? (uint32_t)M : hist[b * KB];     // b*KB <= N for b < NBK
-    PHASE_STAMP(5);
     __syncthreads();
     #pragma unroll
     for (int s = 0; s < E; s++)
@@ -392,14 +370,9 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
         yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
-    PHASE_STAMP(6);
 }
 
-#ifdef QLKA_PHASE_TIMING
-extern "C" int qlka_debug_phase_clocks(long long* out16) {
-    return (int)cudaMemcpyFromSymbol(out16, g_phase_clock, sizeof(long long) * 16);
-}
-#endif
+
 
 template <int THREADS, int E>
 static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {

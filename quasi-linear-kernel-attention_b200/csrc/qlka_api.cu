@@ -14,6 +14,7 @@ size_t      sort_rank_large_scratch_bytes(int nseg, int N, int M);
 cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream);
 cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
 int         walk_lanes_per_stream(int C4);
+int         walk_threads();
 cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st);
 cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st);
 cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t st);
@@ -77,17 +78,19 @@ struct WalkPlan { int sps, segs, nitems, grid; };
 
 WalkPlan plan_walk(int nseg, int N, int C4) {
     const int lps      = walk_lanes_per_stream(C4);
-    const int streams  = 256 / lps;
+    const int streams  = walk_threads() / lps;
     int per_sm = C4 <= 64 ? 2 : 1;              // resident walk CTAs per SM (registers and shared memory)
     if (const char* e = std::getenv("QLKA_WALK_CTAS_PER_SM")) { const int v = std::atoi(e); if (v >= 1 && v <= 8) per_sm = v; }   // tuning aid
     const int grid_cap = sm_count() * per_sm;
     const int nbk      = nblocks(N);
-    int sps_max = 1;
-    while (sps_max * 2 <= streams && sps_max * 2 <= nbk) sps_max *= 2;
+    // streams per segment: a divisor of the CTA's stream count; more of them until there are enough items to
+    // balance the persistent CTAs, but at least four key blocks per stream when the segment allows it
     int sps = 1;
-    // more streams per segment until there are enough items to balance the persistent CTAs,
-    // but keep at least four key blocks per stream when the segment allows it
-    while (sps < sps_max && (long long)nseg * sps / streams < 8LL * grid_cap && nbk / (sps * 2) >= 4) sps *= 2;
+    for (int cand = 2; cand <= streams; cand++) {
+        if (streams % cand || cand > nbk || nbk / cand < 4) continue;
+        if ((long long)nseg * sps / streams >= 8LL * grid_cap) break;
+        sps = cand;
+    }
     WalkPlan w;
     w.sps    = sps;
     w.segs   = streams / sps;

@@ -264,6 +264,7 @@ static cudaError_t launch_lap(const WalkArgs& a, int grid, cudaStream_t stream) 
 
 // lanes per stream for a padded channel count
 int walk_lanes_per_stream(int C4) { return C4 <= 32 ? 8 : 16; }
+int walk_threads() { return WALK_THREADS; }
 
 cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream) {
     if (a.C4 <= 32)  return launch_lap<8, 4>(a, grid, stream);

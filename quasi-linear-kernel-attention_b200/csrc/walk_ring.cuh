@@ -17,7 +17,10 @@
 
 namespace qlka {
 
-constexpr int WALK_THREADS = 256;
+#ifndef QLKA_WALK_THREADS
+#define QLKA_WALK_THREADS 256
+#endif
+constexpr int WALK_THREADS = QLKA_WALK_THREADS;
 #ifndef QLKA_RING_DEPTH
 #define QLKA_RING_DEPTH 2
 #endif

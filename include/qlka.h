@@ -99,6 +99,20 @@ int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v
                                   void* workspace, size_t workspace_bytes,
                                   int P, int D, int N, int M, int C, int path, qlka_stream_t stream);
 
+/* ---- weighted abs sum over shifted queries ---------------------------------------------
+ * out = sum_s weights[s] * abs_sum(q + shifts[s], k, v) for 1 <= n_shifts <= 4 from ONE sort of the keys:
+ * the shifted copies of the queries are ranked together and share their output rows. out_u likewise
+ * (nullable). Needs N <= 16384 and n_shifts * M <= 16384. shifts and weights are host arrays.
+ * With shifts (0, +1, -1) and weights (-1, 1/2, 1/2) this is the whole add_bump numerator and row sum,
+ * which the reference assembles from three separate abs sums
+ * (Experiments/kernel_attention/attention.py:84-92). Forward only. */
+int qlka_abs_shifted_forward_workspace_bytes(int P, int D, int N, int M, int C, int n_shifts, size_t* bytes);
+int qlka_weighted_abs_sum_shifted_forward(const float* q, const float* k, const float* v,
+                                          float* out_w, float* out_u /* nullable */,
+                                          const float* shifts, const float* weights, int n_shifts,
+                                          void* workspace, size_t workspace_bytes,
+                                          int P, int D, int N, int M, int C, qlka_stream_t stream);
+
 /* ---- weighted abs sum, backward --------------------------------------------------------
  * Gradients of sum(out_w * g_w) + sum(out_u * g_u) (g_u NULL: first term only):
  * grad_q (P, D, M), grad_k (P, D, N), grad_v (P, N, C); a key equal to a query has

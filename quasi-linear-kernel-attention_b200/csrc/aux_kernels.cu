@@ -67,11 +67,12 @@ __global__ void __launch_bounds__(256) vecsum_kernel(const float* __restrict__ x
     if (threadIdx.x == 0) out[p] = red[0];
 }
 
-// out[p, m, c] = ktot[p, c] - qsum[p, m] * vsum[p, c];  out_u[p, m] = ksr[p] - Nk * qsum[p, m]
+// out[p, m, c] = A * ktot[p, c] - (A * qsum[p, m] + Bq) * vsum[p, c];  out_u[p, m] = A * ksr[p] - Nk * (A * qsum[p, m] + Bq)
+// (A = 1, Bq = 0 for the plain abs sum; a folded sum over shifted queries has A = sum of weights, Bq = D * sum w_s shift_s)
 __global__ void abs_init_kernel(
     const float* __restrict__ ktot, const float* __restrict__ vsum, const float* __restrict__ qsum,
     const float* __restrict__ ksr, float* __restrict__ out, float* __restrict__ out_u,
-    const int M, const int C4, const float Nk, const long long total4)
+    const int M, const int C4, const float Nk, const long long total4, const float A, const float Bq)
 {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total4) return;
@@ -81,10 +82,10 @@ __global__ void abs_init_kernel(
     const long long p  = pm / M;
     const float4 kt = *reinterpret_cast<const float4*>(ktot + p * C4 + c);
     const float4 vs = *reinterpret_cast<const float4*>(vsum + p * C4 + c);
-    const float  qs = qsum[pm];
+    const float  qs = fmaf(A, qsum[pm], Bq);
     *reinterpret_cast<float4*>(out + pm * C4 + c) =
-        make_float4(fmaf(-qs, vs.x, kt.x), fmaf(-qs, vs.y, kt.y), fmaf(-qs, vs.z, kt.z), fmaf(-qs, vs.w, kt.w));
-    if (out_u && c == 0) out_u[pm] = ksr[p] - Nk * qs;
+        make_float4(fmaf(-qs, vs.x, A * kt.x), fmaf(-qs, vs.y, A * kt.y), fmaf(-qs, vs.z, A * kt.z), fmaf(-qs, vs.w, A * kt.w));
+    if (out_u && c == 0) out_u[pm] = A * ksr[p] - Nk * qs;
 }
 
 // dst (rows, C4) <- src (rows, C), zero filled
@@ -119,9 +120,9 @@ cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t
     return cudaGetLastError();
 }
 cudaError_t launch_abs_init(const float* ktot, const float* vsum, const float* qsum, const float* ksr,
-                            float* out, float* out_u, int P, int M, int C4, int Nk, cudaStream_t st) {
+                            float* out, float* out_u, int P, int M, int C4, int Nk, float A, float Bq, cudaStream_t st) {
     const long long total4 = (long long)P * M * (C4 >> 2);
-    abs_init_kernel<<<blocks_for(total4, 256), 256, 0, st>>>(ktot, vsum, qsum, ksr, out, out_u, M, C4, (float)Nk, total4);
+    abs_init_kernel<<<blocks_for(total4, 256), 256, 0, st>>>(ktot, vsum, qsum, ksr, out, out_u, M, C4, (float)Nk, total4, A, Bq);
     return cudaGetLastError();
 }
 cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st) {

@@ -19,7 +19,7 @@ cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cud
 cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st);
 cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t st);
 cudaError_t launch_abs_init(const float* ktot, const float* vsum, const float* qsum, const float* ksr,
-                            float* out, float* out_u, int P, int M, int C4, int Nk, cudaStream_t st);
+                            float* out, float* out_u, int P, int M, int C4, int Nk, float A, float Bq, cudaStream_t st);
 cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
 cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
 }  // namespace qlka
@@ -133,6 +133,7 @@ WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int n
     a.rows = rows; a.xperm = r.xperm; a.xval = r.xval; a.yrec = r.yrec; a.mstart = r.mstart;
     a.nseg = nseg; a.D = D; a.N = N; a.M = M; a.C4 = C4; a.sps = w.sps; a.nitems = w.nitems;
     a.sign = 1.0f;
+    a.Mrows = M;
     return a;
 }
 
@@ -215,7 +216,7 @@ const char* qlka_status_string(int status) {
         case QLKA_ERR_NULL:              return "a required pointer is NULL";
         case QLKA_ERR_WORKSPACE:         return "workspace too small or not 256-byte aligned";
         case QLKA_ERR_CUDA:              return "a CUDA runtime call failed";
-        case QLKA_ERR_UNSUPPORTED:       return "no kernel in this build for max(N,M) > 16384";
+        case QLKA_ERR_UNSUPPORTED:       return "no kernel in this build for these sizes (shifted abs sum: N and n_shifts * M must be <= 16384)";
         case QLKA_ERR_NO_ALLOC_LIMIT:    return "problem needs more scratch than the fixed 32 MiB of the no-allocation entry point; use the workspace variant";
         default:                         return "unknown status";
     }
@@ -345,6 +346,45 @@ int qlka_abs_forward_workspace_bytes(int P, int D, int N, int M, int C, size_t* 
     return QLKA_OK;
 }
 
+// ns == 0: the plain abs sum. ns >= 1: sum_s weights[s] * abs_sum(q + shifts[s]) from one sort of the keys.
+static int abs_forward_impl(const float* q, const float* k, const float* v, float* out_w, float* out_u,
+                            void* workspace, size_t workspace_bytes, int P, int D, int N, int M, int C,
+                            int ns, const float* shifts, const float* weights, cudaStream_t stream)
+{
+    const int MQ = ns ? ns * M : M;                 // queries per segment
+    AbsFwdWs ws(workspace, P, D, N, MQ, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    const int C4 = round4(C), nseg = P * D;
+    const bool full = out_u != nullptr;
+    float A = 1.0f, Bq = 0.0f;
+    if (ns) { A = 0.0f; for (int s = 0; s < ns; s++) { A += weights[s]; Bq += weights[s] * shifts[s] * (float)D; } }
+
+    const float* rows = v;
+    float*       out  = out_w;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        rows = ws.vpad; out = ws.opad;
+    }
+    // rank-1 part: out = k_total - qsum * vsum, out_u = ksum_raw - N * qsum (weighted over the shifts when folded)
+    CU(launch_colsum_d(q, ws.qsum, P, D, M, stream));
+    CU(launch_colsum_d(k, ws.ksumd, P, D, N, stream));
+    CU(cudaMemsetAsync(ws.vsum, 0, sizeof(float) * ((size_t)P * C4 * 2 + P), stream));
+    CU(launch_rowstat(rows, ws.ksumd, ws.vsum, ws.ktot, ws.ksr, P, N, C4, stream));
+    CU(launch_abs_init(ws.ktot, ws.vsum, ws.qsum, ws.ksr, out, out_u, P, M, C4, N, A, Bq, stream));
+
+    SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, MQ, MODE_ABS, full ? SCAL_UNIT : SCAL_NONE);
+    s.out_u = out_u; s.rows_coef = 1;
+    if (ns) { s.fold = M; for (int i = 0; i < ns; i++) { s.shift[i] = shifts[i]; s.wgt[i] = weights[i]; } }
+    CU(launch_sort_rank(s, ws.rec, stream));
+
+    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, MQ, C4);
+    w.out = out; w.Mrows = M;
+    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid, stream));
+
+    if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
+    return QLKA_OK;
+}
+
 int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v,
                                   float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
                                   int P, int D, int N, int M, int C, int path, qlka_stream_t stream_)
@@ -354,35 +394,32 @@ int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v
     if (path < -1 || path > 1) return QLKA_ERR_PATH;
     if (path == 1 && (N > 4096 || M > 4096)) return QLKA_ERR_FUSED_UNAVAILABLE;
     if (!q || !k || !v || !out_w) return QLKA_ERR_NULL;
-    AbsFwdWs ws(workspace, P, D, N, M, C);
-    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
-    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-    const int C4 = round4(C), nseg = P * D;
-    const bool full = out_u != nullptr;
+    return abs_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C, 0, nullptr, nullptr,
+                            reinterpret_cast<cudaStream_t>(stream_));
+}
 
-    const float* rows = v;
-    float*       out  = out_w;
-    if (C4 != C) {
-        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
-        rows = ws.vpad; out = ws.opad;
-    }
-    // rank-1 part: out = k_total - qsum * vsum, out_u = ksum_raw - N * qsum
-    CU(launch_colsum_d(q, ws.qsum, P, D, M, stream));
-    CU(launch_colsum_d(k, ws.ksumd, P, D, N, stream));
-    CU(cudaMemsetAsync(ws.vsum, 0, sizeof(float) * ((size_t)P * C4 * 2 + P), stream));
-    CU(launch_rowstat(rows, ws.ksumd, ws.vsum, ws.ktot, ws.ksr, P, N, C4, stream));
-    CU(launch_abs_init(ws.ktot, ws.vsum, ws.qsum, ws.ksr, out, out_u, P, M, C4, N, stream));
-
-    SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_ABS, full ? SCAL_UNIT : SCAL_NONE);
-    s.out_u = out_u;
-    CU(launch_sort_rank(s, ws.rec, stream));
-
-    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
-    w.out = out;
-    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid, stream));
-
-    if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
+int qlka_abs_shifted_forward_workspace_bytes(int P, int D, int N, int M, int C, int n_shifts, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    if (n_shifts < 1 || n_shifts > 4) return QLKA_ERR_BAD_SHAPE;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if ((long long)n_shifts * M > SMALL_MAX || N > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;
+    *bytes = AbsFwdWs(nullptr, P, D, N, n_shifts * M, C).bytes;
     return QLKA_OK;
+}
+
+int qlka_weighted_abs_sum_shifted_forward(const float* q, const float* k, const float* v,
+                                          float* out_w, float* out_u, const float* shifts, const float* weights, int n_shifts,
+                                          void* workspace, size_t workspace_bytes,
+                                          int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    if (n_shifts < 1 || n_shifts > 4) return QLKA_ERR_BAD_SHAPE;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if ((long long)n_shifts * M > SMALL_MAX || N > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;
+    if (!q || !k || !v || !out_w || !shifts || !weights) return QLKA_ERR_NULL;
+    return abs_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C, n_shifts, shifts, weights,
+                            reinterpret_cast<cudaStream_t>(stream_));
 }
 
 // ---------------------------------------------------------------- abs backward
@@ -444,7 +481,7 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
         WalkPlan plan = plan_walk(nseg, M, C4);
         // one walk for both: grad_v = abs sum with keys q, weights g_w, evaluated at the keys k (row reductions on
         // top of its rank-1 initial value); grad_k = prefix of g_w rows contracted with v rows (+ the g_u term in e1)
-        CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, stream));
+        CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, 1.0f, 0.0f, stream));
         WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
         w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k; w.out = gv;
         CU(launch_prefix_walk(w, EMIT_BOTH, plan.grid, stream));

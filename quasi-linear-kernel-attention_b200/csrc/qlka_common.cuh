@@ -52,6 +52,11 @@ struct SortArgs {
     const float* us;         // (P, N)  SCAL_PREFIX
     const float* us_total;   // (P)     SCAL_PREFIX
     int nseg, D, N, M, mode, scal;
+    // folded queries (abs mode): the M queries are `M / fold` shifted copies of the `fold` values at y, copy s being
+    // y + shift[s] with weight wgt[s]; records carry the weight and point at row m % fold. fold = 0: off.
+    int   fold;
+    float shift[4], wgt[4];
+    int   rows_coef;          // abs mode: 1 = e1 is the key-sum coefficient -2 * weight of the row emission, 0 = e1 is a dot addend
 };
 
 struct WalkArgs {
@@ -68,6 +73,7 @@ struct WalkArgs {
     float*          out_s;    // emit dot: (P, D, M) plain stores
     float           sign;     // emit dot: output scale (+1 gradients, -1 public sgn op)
     int nseg, D, N, M, C4, sps, nitems;
+    int Mrows;                // rows of `out` per p (= M unless the queries are folded)
 };
 
 __device__ __forceinline__ uint32_t f2key(float f) {

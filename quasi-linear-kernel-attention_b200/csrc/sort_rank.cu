@@ -305,7 +305,9 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();
-    const float* ysrc = a.y + (long long)seg * M;
+    const int    MR   = a.fold ? a.fold : M;          // distinct query values (and output rows) per segment
+    const float* ysrc = a.y + (long long)seg * MR;
+    auto yval = [&](int m) -> float { return a.fold ? ysrc[m % MR] + a.shift[m / MR] : ysrc[m]; };
     uint32_t rp[E];                                   // rank, later rank | position << 16 (both <= 16384)
     // branch-free binary search, QI queries in flight per thread (the probes are latency bound)
     constexpr int QI = E >= 8 ? 8 : 4;
@@ -316,7 +318,7 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
         #pragma unroll
         for (int t = 0; t < QI; t++) {
             const int m = tid + (s0 + t) * THREADS;
-            yq[t]   = m < M ? ysrc[m] : 0.0f;
+            yq[t]   = m < M ? yval(m) : 0.0f;
             posq[t] = 0;
         }
         #pragma unroll
@@ -354,20 +356,22 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
     for (int pos = tid; pos < M; pos += THREADS) {
         const uint32_t w = who[pos];
         const int      m = (int)(w & 0xffffu), r = (int)(w >> 16);
-        const float    y = ysrc[m];
+        const float    y   = yval(m);
+        const int      row = a.fold ? m % MR : m;
+        const float    wq  = a.fold ? a.wgt[m / MR] : 1.0f;
         float e0 = 0.0f, e1 = 0.0f;
         if (a.mode == MODE_LAPLACE) {
             e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
             e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
             if (a.scal == SCAL_UNIT)
-                atomicAdd(a.out_u + (long long)p * M + m, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+                atomicAdd(a.out_u + (long long)p * MR + row, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
         } else {
-            if (a.mode == MODE_ABS) e0 = 2.0f * y;
-            if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
+            if (a.mode == MODE_ABS) { e0 = 2.0f * y * wq; e1 = a.rows_coef ? -2.0f * wq : 0.0f; }      // row emission: e0 * PV + e1 * PK
+            if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * MR + row, wq * 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
             else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
             else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
         }
-        yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
+        yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)row, (uint32_t)r);
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
 }

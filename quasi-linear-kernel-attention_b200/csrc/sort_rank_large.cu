@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(256) rank_records(
     const float* su0 = a.su0 + seg * (N + 1);
     const float* su1 = a.su1 + seg * (N + 1);
     const float    y   = key2f(ysorted[seg * mpd + m]);
-    const uint32_t row = yidx[seg * mpd + m];
+    const uint32_t row = yidx[seg * mpd + m];       // (folded queries are not supported on this path; the host refuses them)
     const int      r   = lower_bound_g(xs, N, y);
     float e0 = 0.0f, e1 = 0.0f;
     if (a.mode == MODE_LAPLACE) {
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(256) rank_records(
         if (a.scal == SCAL_UNIT)
             atomicAdd(a.out_u + (long long)p * M + row, (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
     } else {
-        if (a.mode == MODE_ABS) e0 = 2.0f * y;
+        if (a.mode == MODE_ABS) { e0 = 2.0f * y; e1 = a.rows_coef ? -2.0f : 0.0f; }
         if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + row, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
         else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + row] * (2.0f * (float)r - (float)N);
         else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];

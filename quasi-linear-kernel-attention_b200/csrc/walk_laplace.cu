@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
         f.rows   = a.rows + (long long)p * N * C4 + c0l;
         f.mstart = a.mstart + (long long)sg * mstride(N);
         f.yrec   = a.yrec + (long long)sg * (M + 1);
-        float*          out  = a.out + (long long)p * M * C4 + c0l;
+        float*          out  = a.out + (long long)p * a.Mrows * C4 + c0l;
         const long long slot = (long long)blockIdx.x * SEGS + sl;
         float*          ck   = a.ckpt + slot * NBK * C4 + c0l;
         float*          wk   = a.wck + slot * NBK;

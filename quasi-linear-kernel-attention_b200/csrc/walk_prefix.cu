@@ -1,8 +1,9 @@
 // Prefix walk: for every query m of every segment, with r its rank among the sorted keys,
 // PV = sum of the rows of the r keys below it and PK = sum of key * row over the same keys:
 //
-//   EMIT_ROWS  out[p, row_m, :] += e0_m * PV - 2 * PK          (vector reductions)
-//              with e0 = 2 * query this is the walk term 2 (q PV - PK) of the abs sum
+//   EMIT_ROWS  out[p, row_m, :] += e0_m * PV + e1_m * PK       (vector reductions)
+//              with e0 = 2 * query and e1 = -2 this is the walk term 2 (q PV - PK) of the abs sum; folded
+//              queries (shifted, weighted copies that share a row) scale both by their weight
 //              (Weighted_Abs_Sum/csrc/abs_kernels.cu:9-18; abs_chunk :78-199, abs_prefix :202-405)
 //   EMIT_BOTH  both of the others from one walk (grad_v and grad_k share stream, rows and queries)
 //   EMIT_DOT   out_s[seg, row_m] = sign * ( <g[p, row_m, :], 2 PV - wtotal[p, :]> + e1_m )
@@ -134,7 +135,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 wt.x[c] = t.x; wt.x[c + 1] = t.y; wt.x[c + 2] = t.z; wt.x[c + 3] = t.w;
             }
         }
-        float*       out   = DO_ROWS ? a.out + (long long)p * M * C4 + c0l : nullptr;
+        float*       out   = DO_ROWS ? a.out + (long long)p * a.Mrows * C4 + c0l : nullptr;
         const float* g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
         float*       out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
 
@@ -176,15 +177,16 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 auto emit = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq, const Vec<CPL>& gq) {
                     if (DO_ROWS) {
                         const float e0 = __uint_as_float(rec.x);
+                        const float ek = EMIT == EMIT_ROWS ? __uint_as_float(rec.y) : -2.0f;     // (rec.y is the dot term's addend in EMIT_BOTH)
                         if (on) {
                             float* o = out + (size_t)rec.z * C4;
                             #pragma unroll
                             for (int c = 0; c < CPL; c += 4)
                                 red_add4(o + c,
-                                         fmaf(e0, Pq.x[c],     -2.0f * Kq.x[c]),
-                                         fmaf(e0, Pq.x[c + 1], -2.0f * Kq.x[c + 1]),
-                                         fmaf(e0, Pq.x[c + 2], -2.0f * Kq.x[c + 2]),
-                                         fmaf(e0, Pq.x[c + 3], -2.0f * Kq.x[c + 3]));
+                                         fmaf(e0, Pq.x[c],     ek * Kq.x[c]),
+                                         fmaf(e0, Pq.x[c + 1], ek * Kq.x[c + 1]),
+                                         fmaf(e0, Pq.x[c + 2], ek * Kq.x[c + 2]),
+                                         fmaf(e0, Pq.x[c + 3], ek * Kq.x[c + 3]));
                         }
                     }
                     if (DO_DOT) {

@@ -45,6 +45,10 @@ def lib():
         L.qlka_weighted_laplace_sum_forward_noalloc.argtypes = [_vp] * 5 + [_i] * 5 + [_vp]
         L.qlka_weighted_abs_sum_forward.restype = _i
         L.qlka_weighted_abs_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 6 + [_vp]
+        L.qlka_abs_shifted_forward_workspace_bytes.restype = _i
+        L.qlka_abs_shifted_forward_workspace_bytes.argtypes = [_i] * 6 + [ctypes.POINTER(_sz)]
+        L.qlka_weighted_abs_sum_shifted_forward.restype = _i
+        L.qlka_weighted_abs_sum_shifted_forward.argtypes = [_vp] * 5 + [ctypes.POINTER(ctypes.c_float)] * 2 + [_i] + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_weighted_abs_sum_backward.restype = _i
         L.qlka_weighted_abs_sum_backward.argtypes = [_vp] * 8 + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_weighted_sgn_sum_forward.restype = _i
@@ -231,6 +235,30 @@ def abs_forward(q, k, v, full, path=-1):
         st = L.qlka_weighted_abs_sum_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(),
                                              out_u.data_ptr() if full else None,
                                              ws.data_ptr(), n, P, D, N, M, C, int(path), _stream())
+    if st:
+        _raise(st)
+    return out_w, out_u
+
+
+def abs_shifted_forward(q, k, v, shifts, weights, full=True):
+    """sum_s weights[s] * abs_sum(q + shifts[s], k, v) from one sort of the keys: (out_w, out_u or None)."""
+    P, D, N, M, C = check_qkv(q, k, v, "q, k, and v")
+    ns = len(shifts)
+    _check(len(weights) == ns and 1 <= ns <= 4, "shifts and weights must have the same length, 1 to 4")
+    L = lib()
+    sh = (ctypes.c_float * ns)(*[float(x) for x in shifts])
+    wg = (ctypes.c_float * ns)(*[float(x) for x in weights])
+    with torch.cuda.device(q.device):
+        n = _sz(0)
+        st = L.qlka_abs_shifted_forward_workspace_bytes(P, D, N, M, C, ns, ctypes.byref(n))
+        if st:
+            _raise(st)
+        ws = torch.empty(max(int(n.value), 256), dtype=torch.uint8, device=q.device)
+        out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
+        out_u = torch.empty(P, M, dtype=torch.float32, device=q.device) if full else None
+        st = L.qlka_weighted_abs_sum_shifted_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(),
+                                                     out_u.data_ptr() if full else None, sh, wg, ns,
+                                                     ws.data_ptr(), int(n.value), P, D, N, M, C, _stream())
     if st:
         _raise(st)
     return out_w, out_u

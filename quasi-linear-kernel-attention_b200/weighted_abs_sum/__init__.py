@@ -5,6 +5,7 @@ from weighted_abs_sum.ops import (
     weighted_abs_sum,
     weighted_abs_sum_full,
     weighted_sgn_sum,
+    weighted_abs_sum_shifted,
     set_keops_cutoff,
 )
 
@@ -12,5 +13,6 @@ __all__ = [
     "weighted_abs_sum",
     "weighted_abs_sum_full",
     "weighted_sgn_sum",
+    "weighted_abs_sum_shifted",
     "set_keops_cutoff",
 ]

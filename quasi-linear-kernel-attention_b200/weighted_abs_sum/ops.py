@@ -84,6 +84,13 @@ def weighted_abs_sum_full(q, k, v, backend="auto"):
     return _WeightedAbsSumFull.apply(q, k, v, _resolve(backend))
 
 
+def weighted_abs_sum_shifted(q, k, v, shifts, weights):
+    """(out_w, out_u) of sum_s weights[s] * weighted_abs_sum_full(q + shifts[s], k, v), evaluated with one
+    sort of the keys (at most 4 shifts, N <= 16384, len(shifts) * M <= 16384). Not in the reference, whose
+    add_bump calls the abs sum three times; forward only (no autograd)."""
+    return _native.abs_shifted_forward(q, k, v, shifts, weights, full=True)
+
+
 def weighted_sgn_sum(q, k, v, g, backend="auto"):
     """out[p,d,m] = sum_n sgn(k[p,d,n] - q[p,d,m]) * dot(v[p,n,:], g[p,m,:])   (P, D, M).
 

@@ -149,3 +149,20 @@ def test_argument_errors():
         weighted_sgn_sum(q, k, v, torch.zeros(1, 5000, 4, device="cuda"), backend="cuda-fused")
     with pytest.raises(RuntimeError, match="CUDA tensors"):
         weighted_abs_sum(q.cpu(), k.cpu(), v.cpu())
+
+
+@pytest.mark.parametrize("shape", [(2, 3, 50, 40, 4), (3, 4, 600, 600, 64), (1, 2, 3000, 5000, 33)])
+def test_shifted_sum_equals_separate_sums(shape):
+    """The folded entry point against three separate abs sums, and the fused add_bump against float64."""
+    from weighted_abs_sum import weighted_abs_sum_full, weighted_abs_sum_shifted
+    P, D, N, M, C = shape
+    q, k, v = make_inputs(P, D, N, M, C, seed=N + M, scale=1.0)
+    shifts, weights = (0.0, 1.0, -1.0), (-1.0, 0.5, 0.5)
+    w, u = weighted_abs_sum_shifted(q, k, v, shifts, weights)
+    rw = sum(wt * sorted_scan.abs_sum(q + sh, k, v)[0] for sh, wt in zip(shifts, weights))
+    ru = sum(wt * sorted_scan.abs_sum(q + sh, k, v)[1] for sh, wt in zip(shifts, weights))
+    assert rel_err(w, rw) < TOL, rel_err(w, rw)
+    assert rel_err(u, ru) < TOL, rel_err(u, ru)
+    w2, u2 = weighted_abs_sum_shifted(q, k, v, (0.25,), (2.0,))
+    a, b = sorted_scan.abs_sum(q + 0.25, k, v)
+    assert rel_err(w2, 2 * a) < TOL and rel_err(u2, 2 * b) < TOL

@@ -41,7 +41,7 @@ def measured_peaks():
 
 
 # ------------------------------------------------------------------ CPU baseline (reference path restated)
-def cpu_baseline(p_sample=1, m_sample=4096, repeats=1):
+def cpu_baseline(p_sample=1, m_sample=16384, repeats=1):
     from oracle import chunked_ref
     g = torch.Generator().manual_seed(0)
     q = torch.randn(p_sample, D, m_sample, generator=g) * 2
@@ -191,9 +191,9 @@ def run_ours(args, rank, world, local_rank):
     achieved_op = ALGO_BYTES / (ms * 1e-3) / 1e9
     # dominant kernel: the walk (60 % of the device time, profiles/); its launch time is measured live
     achieved = ALGO_BYTES / (stage["walk_ms"] * 1e-3) / 1e9
-    # DRAM traffic of one walk launch: ncu capture at B=1 (1375 MB, profiles/laplace_forward_b1_h12_n16384_ncu.md),
-    # scaled by the batch because every array the kernel touches grows in proportion to P
-    traffic = 1375e6 * B
+    # DRAM traffic of one walk launch: dram__bytes_read + dram__bytes_write of an ncu capture at the benchmark size
+    # (5.99 GB at B=4, profiles/laplace_forward_b4_h12_n16384_ncu.md); other batches scale it, every array grows with P
+    traffic = 5.99e9 * B / 4
     line = {
         "metric": "q.k pairs/s", "value": pairs / (ms * 1e-3), "unit": "pairs/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,

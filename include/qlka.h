@@ -47,7 +47,7 @@ const char* qlka_status_string(int status);
 /* cudaError_t of the last failing runtime call made by this library on the calling thread. */
 int qlka_last_cuda_error(void);
 
-/* ---- weighted Laplace sum, forward only ------------------------------------------------
+/* ---- weighted Laplace sum, forward ------------------------------------------------------
  * out_w[p,m,c] = sum_{d,n} exp(-|k[p,d,n] - q[p,d,m]|) v[p,n,c]     (P, M, C)
  * out_u[p,m]   = sum_{d,n} exp(-|k[p,d,n] - q[p,d,m]|)              (P, M)
  * Replaces weighted_laplace_sum_forward, Weighted_Laplace_Sum/csrc/binding.cpp:63-100
@@ -85,6 +85,21 @@ int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v
                                   void* workspace, size_t workspace_bytes,
                                   int P, int D, int N, int M, int C, qlka_stream_t stream,
                                   float* sort_ms, float* walk_ms);
+
+/* ---- weighted Laplace sum, backward -----------------------------------------------------
+ * Gradients of sum(out_w * g_w) + sum(out_u * g_u) (g_u NULL: first term only):
+ * grad_q (P, D, M), grad_k (P, D, N), grad_v (P, N, C), from two more sort/rank runs and two
+ * walks. exp(-|k - q|) has no derivative where a key equals a query; there both grad_q and
+ * grad_k take the one-sided derivative +1 of the side the walk puts ties on (torch autograd
+ * through exp(-abs(x)) takes 0 there). The reference has no counterpart: its Laplace operator
+ * is forward only and training goes through the chunked PyTorch path
+ * (Experiments/kernel_attention/attention.py:110-115). */
+int qlka_laplace_backward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes);
+int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const float* v,
+                                       const float* g_w, const float* g_u /* nullable */,
+                                       float* grad_q, float* grad_k, float* grad_v,
+                                       void* workspace, size_t workspace_bytes,
+                                       int P, int D, int N, int M, int C, qlka_stream_t stream);
 
 /* ---- weighted abs sum, forward ---------------------------------------------------------
  * out_w[p,m,c] = sum_{d,n} |k[p,d,n] - q[p,d,m]| v[p,n,c]           (P, M, C)

@@ -122,6 +122,38 @@ def abs_sum_backward(q, k, v, g_w, g_u=None):
     return grad_q, grad_k, grad_v
 
 
+def laplace_sum_backward(q, k, v, g_w, g_u=None):
+    """Gradients (grad_q (P,D,M), grad_k (P,D,N), grad_v (P,N,C)) of sum(out_w * g_w) + sum(out_u * g_u)
+    for the Laplace sum, float64. Where k == q the kernel exp(-|k - q|) has no derivative; the sorted walk
+    counts a tied key on the upper side of the query, E = exp(-(k - q)), in both of its runs, so
+    dE/dq = +1 and (roles swapped) dE/dk = +1 there. The reference has no Laplace backward; away from
+    ties this is the autograd gradient of its chunked PyTorch route
+    (Experiments/kernel_attention/attention.py:110-115)."""
+    q, k, v, g_w = _f64(q, k, v, g_w)
+    P, D, M = q.shape
+    N, C = k.shape[2], v.shape[2]
+    gu = None if g_u is None else _f64(g_u)[0]
+    grad_q = torch.empty(P, D, M, dtype=torch.float64)
+    grad_k = torch.zeros(P, D, N, dtype=torch.float64)
+    grad_v = torch.zeros(P, N, C, dtype=torch.float64)
+    starts, mc = _chunks(D, N, M)
+    for p in range(P):
+        for m0 in starts:
+            qq = q[p, :, m0:m0 + mc]
+            diff = k[p][:, None, :] - qq[:, :, None]                        # (D, mc, N) = k - q
+            E = (-diff.abs()).exp()
+            B = g_w[p, m0:m0 + mc] @ v[p].T                                 # (mc, N) <g_m, v_n>
+            if gu is not None:
+                B = B + gu[p, m0:m0 + mc, None]
+            # dE/dq = +E if k >= q else -E;  dE/dk = +E if q >= k else -E
+            sq = torch.where(diff >= 0, E, -E)
+            sk = torch.where(diff <= 0, E, -E)
+            grad_q[p, :, m0:m0 + mc] = (sq * B[None]).sum(2)
+            grad_k[p] += (sk * B[None]).sum(1)
+            grad_v[p] += E.sum(0).T @ g_w[p, m0:m0 + mc]
+    return grad_q, grad_k, grad_v
+
+
 # ---------------------------------------------------------------- attention algebra
 
 EPS = 1e-3      # Riesz offset (Experiments/kernel_attention/kernels.py:9)

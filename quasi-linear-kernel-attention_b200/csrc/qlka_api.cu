@@ -11,7 +11,7 @@ namespace qlka {
 cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
 cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_t stream);
 size_t      sort_rank_large_scratch_bytes(int nseg, int N, int M);
-cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream);
+cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
 cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
 int         walk_lanes_per_stream(int C4);
 int         walk_threads();
@@ -161,6 +161,28 @@ struct LaplaceWs {
     }
 };
 
+// ------------------------------------------------------------------ Laplace backward
+struct LaplaceBwdWs {
+    float *vpad, *gpad, *gvpad; Records rec; float* ckpt; float* wck; WalkPlan plan_k, plan_q; size_t bytes;
+    LaplaceBwdWs(void* base, int P, int D, int N, int M, int C) {
+        Bump b(base);
+        const int C4 = round4(C), nseg = P * D;
+        vpad  = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        gpad  = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
+        gvpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
+        const int mx = N > M ? N : M;
+        rec.carve(b, nseg, mx, mx);
+        plan_k = plan_walk(nseg, N, C4);        // stream of keys k (grad_q)
+        plan_q = plan_walk(nseg, M, C4);        // stream of keys q (grad_v, grad_k)
+        const size_t slots_k = (size_t)plan_k.grid * plan_k.segs * nblocks(N);
+        const size_t slots_q = (size_t)plan_q.grid * plan_q.segs * nblocks(M);
+        const size_t slots   = slots_k > slots_q ? slots_k : slots_q;
+        ckpt = b.take<float>(slots * C4);
+        wck  = b.take<float>(slots);
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+
 // ------------------------------------------------------------------ abs forward
 struct AbsFwdWs {
     float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr; WalkPlan plan; size_t bytes;
@@ -261,7 +283,7 @@ static int laplace_forward_impl(const float* q, const float* k, const float* v,
 
     WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
     w.ckpt = ws.ckpt; w.wck = ws.wck; w.out = out;
-    CU(launch_laplace_walk(w, ws.plan.grid, stream));
+    CU(launch_laplace_walk(w, EMIT_ROWS, ws.plan.grid, stream));
     if (ev) CU(cudaEventRecord(ev[2], stream));
 
     if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
@@ -294,6 +316,64 @@ int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v
     }
     for (int i = 0; i < 3; i++) cudaEventDestroy(ev[i]);
     return st;
+}
+
+// ---------------------------------------------------------------- Laplace backward
+int qlka_laplace_backward_workspace_bytes(int P, int D, int N, int M, int C, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    *bytes = LaplaceBwdWs(nullptr, P, D, N, M, C).bytes;
+    return QLKA_OK;
+}
+
+int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const float* v,
+                                       const float* g_w, const float* g_u,
+                                       float* grad_q, float* grad_k, float* grad_v,
+                                       void* workspace, size_t workspace_bytes,
+                                       int P, int D, int N, int M, int C, qlka_stream_t stream_)
+{
+    int st = check_dims(P, D, N, M, C);
+    if (st) return st;
+    if (!q || !k || !v || !g_w || !grad_q || !grad_k || !grad_v) return QLKA_ERR_NULL;
+    LaplaceBwdWs ws(workspace, P, D, N, M, C);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int C4 = round4(C), nseg = P * D;
+    const bool full = g_u != nullptr;
+
+    const float* vrows = v;
+    const float* grows = g_w;
+    float*       gv    = grad_v;
+    if (C4 != C) {
+        CU(launch_pad_rows(v, ws.vpad, (long long)P * N, C, C4, stream));
+        CU(launch_pad_rows(g_w, ws.gpad, (long long)P * M, C, C4, stream));
+        vrows = ws.vpad; grows = ws.gpad; gv = ws.gvpad;
+    }
+    CU(cudaMemsetAsync(gv, 0, sizeof(float) * (size_t)P * N * C4, stream));
+    if (!full) {    // the walks add to grad_q and grad_k; with g_u the sort/rank kernel stores its term there first
+        CU(cudaMemsetAsync(grad_q, 0, sizeof(float) * (size_t)nseg * M, stream));
+        CU(cudaMemsetAsync(grad_k, 0, sizeof(float) * (size_t)nseg * N, stream));
+    }
+    {   // grad_q[d, m] = <g_w[m], e1 R_r - e0 L_{r-1}> + g_u[m] (e1 Ru_r - e0 Lu_{r-1}): queries q walk the key stream k
+        SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_LAPLACE, full ? SCAL_SIGNED : SCAL_NONE);
+        s.uq = g_u; s.out_s = grad_q;
+        CU(launch_sort_rank(s, ws.rec, stream));
+        WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
+        w.ckpt = ws.ckpt; w.wck = ws.wck; w.g = grows; w.out_s = grad_q;
+        CU(launch_laplace_walk(w, EMIT_DOT, ws.plan_k.grid, stream));
+    }
+    {   // roles swapped: queries k walk the stream q whose rows are g_w (and whose per-key scalar is g_u);
+        // the row emission is grad_v, the dot with the v rows is grad_k
+        SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_LAPLACE, full ? SCAL_SIGNED : SCAL_NONE);
+        s.us = g_u; s.out_s = grad_k;
+        CU(launch_sort_rank(s, ws.rec, stream));
+        WalkArgs w = walk_args(ws.rec, ws.plan_q, grows, nseg, D, M, N, C4);
+        w.ckpt = ws.ckpt; w.wck = ws.wck; w.g = vrows; w.out_s = grad_k; w.out = gv;
+        CU(launch_laplace_walk(w, EMIT_BOTH, ws.plan_q.grid, stream));
+    }
+    if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
+    return QLKA_OK;
 }
 
 // ---------------------------------------------------------------- Laplace, fixed scratch

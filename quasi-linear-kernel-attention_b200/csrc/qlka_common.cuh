@@ -35,7 +35,9 @@ enum ScalMode : int {
     SCAL_NONE = 0,
     SCAL_UNIT = 1,      // accumulate the v == 1 column of the sum into out_u[p, row]
     SCAL_RANK = 2,      // e1 = uq[p, row] * (2 rank - N)
-    SCAL_PREFIX = 3     // e1 = 2 * (sum of us over keys below) - us_total[p]
+    SCAL_PREFIX = 3,    // e1 = 2 * (sum of us over keys below) - us_total[p]
+    SCAL_SIGNED = 4     // Laplace: out_s[seg, row] = uq[p, row] * (e1 * R_r - e0 * L_{r-1}) with L, R the decayed prefix and
+                        // suffix sums of the per-key scalar us[p, key row]; a null us or uq stands for all ones
 };
 
 struct SortArgs {
@@ -48,9 +50,10 @@ struct SortArgs {
     float*       su0;        // [seg][N + 1] scratch for the scalar scans
     float*       su1;
     float*       out_u;      // (P, M)  SCAL_UNIT
-    const float* uq;         // (P, M)  SCAL_RANK
-    const float* us;         // (P, N)  SCAL_PREFIX
+    const float* uq;         // (P, M)  SCAL_RANK, SCAL_SIGNED
+    const float* us;         // (P, N)  SCAL_PREFIX, SCAL_SIGNED
     const float* us_total;   // (P)     SCAL_PREFIX
+    float*       out_s;      // (nseg, M)  SCAL_SIGNED
     int nseg, D, N, M, mode, scal;
     // folded queries (abs mode): the M queries are `M / fold` shifted copies of the `fold` values at y, copy s being
     // y + shift[s] with weight wgt[s]; records carry the weight and point at row m % fold. fold = 0: off.
@@ -68,10 +71,10 @@ struct WalkArgs {
     float*          ckpt;     // Laplace: [cta slot][NBK][C4] suffix checkpoints
     float*          wck;      // Laplace: [cta slot][NBK]
     float*          out;      // emit rows: (P, M, C4), accumulated with vector reductions
-    const float*    g;        // emit dot: (P, M, C4) matrix contracted with the prefix
-    const float*    wtotal;   // emit dot: (P, C4) column sums of rows
-    float*          out_s;    // emit dot: (P, D, M) plain stores
-    float           sign;     // emit dot: output scale (+1 gradients, -1 public sgn op)
+    const float*    g;        // emit dot: (P, M, C4) matrix contracted with the walk state
+    const float*    wtotal;   // emit dot, prefix walk: (P, C4) column sums of rows
+    float*          out_s;    // emit dot: (P, D, M); plain stores in the prefix walk, added to in the Laplace walk
+    float           sign;     // emit dot, prefix walk: output scale (+1 gradients, -1 public sgn op)
     int nseg, D, N, M, C4, sps, nitems;
     int Mrows;                // rows of `out` per p (= M unless the queries are folded)
 };

@@ -205,7 +205,8 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 // cursor), which also yields mstart for free; the records are then built in position order. Queries of
 // equal rank come out in arbitrary order,
 // which the walk does not care about.
-template <int THREADS, int E>
+// SIGNED builds the SCAL_SIGNED side channel in (a separate instance keeps its registers out of the others).
+template <int THREADS, int E, bool SIGNED>
 __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
 {
     constexpr int CAP = THREADS * E;
@@ -271,16 +272,22 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
             for (int k = 0; k < R; k++) bx[k] = dk[k];
             flush(bx, xval);
             for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
-            if (a.scal == SCAL_UNIT) {
-                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
+            if (a.scal == SCAL_UNIT || (SIGNED && a.scal == SCAL_SIGNED)) {
+                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)) u_i,  su1[j] = sum_{i>=j} exp(-(k_i - k_j)) u_i, with u == 1 or the
+                // per-key scalar, which waits in the staging buffer (own run only) because su0s overwrites the index payload
+                const float* us = (SIGNED && a.scal == SCAL_SIGNED && a.us) ? a.us + (long long)p * N : nullptr;
+                if (us) {
+                    #pragma unroll
+                    for (int k = 0; k < R; k++) if (k < cntk) stage[i0 + k] = us[sidx[i0 + k]];
+                }
                 #pragma unroll
-                for (int k = 0; k < R; k++) bx[k] = 1.0f;
+                for (int k = 0; k < R; k++) bx[k] = us ? (k < cntk ? stage[i0 + k] : 0.0f) : 1.0f;
                 block_affine_scan<THREADS, R, false, 0>(cntk, dk, bx, wa, wb);
                 #pragma unroll
                 for (int k = 0; k < R; k++) if (k < cntk) su0s[i0 + k] = bx[k];     // stays in shared memory
-                // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
+                // backward over the same runs: R_j = a_{j+1} R_{j+1} + u_j
                 #pragma unroll
-                for (int k = 0; k < R; k++) bx[k] = 1.0f;
+                for (int k = 0; k < R; k++) bx[k] = us ? (k < cntk ? stage[i0 + k] : 0.0f) : 1.0f;
                 block_affine_scan<THREADS, R, true, 1>(cntk, dk, bx, wa, wb);
                 flush(bx, su1);
             }
@@ -365,6 +372,9 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
             e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
             if (a.scal == SCAL_UNIT)
                 atomicAdd(a.out_u + (long long)p * MR + row, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+            else if (SIGNED && a.scal == SCAL_SIGNED)
+                a.out_s[(long long)seg * M + m] = (a.uq ? a.uq[(long long)p * M + m] : 1.0f)
+                                                * ((r < N ? e1 * su1[r] : 0.0f) - (r > 0 ? e0 * su0s[r - 1] : 0.0f));
         } else {
             if (a.mode == MODE_ABS) { e0 = 2.0f * y * wq; e1 = a.rows_coef ? -2.0f * wq : 0.0f; }      // row emission: e0 * PV + e1 * PK
             if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * MR + row, wq * 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
@@ -378,16 +388,21 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
 
 
 
-template <int THREADS, int E>
-static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
+template <int THREADS, int E, bool SIGNED>
+static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
-    auto kern = sort_rank_small<THREADS, E>;
+    auto kern = sort_rank_small<THREADS, E, SIGNED>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<a.nseg, THREADS, smem, stream>>>(a);
     return cudaGetLastError();
+}
+
+template <int THREADS, int E>
+static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
+    return a.scal == SCAL_SIGNED ? launch_inst<THREADS, E, true>(a, stream) : launch_inst<THREADS, E, false>(a, stream);
 }
 
 // max(N, M) <= 16384

@@ -159,12 +159,12 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
     if (a.mode != MODE_SGN)
         for (int j = tid; j < NP + KB; j += LT)
             xval[j] = a.mode == MODE_LAPLACE ? (j < N ? dec(j) : 1.0f) : (j < N ? xs[j] : 0.0f);
-    if (a.scal != SCAL_UNIT && a.scal != SCAL_PREFIX) return;
+    if (a.scal != SCAL_UNIT && a.scal != SCAL_PREFIX && a.scal != SCAL_SIGNED) return;
 
     // x_j = A_j x_{j-1} + B_j over the segment, forward (into su0) and, for the Laplace unit column,
     // backward (into su1); a tile at a time with the state carried in shared memory
     const bool   lap = a.mode == MODE_LAPLACE;
-    const float* us  = a.scal == SCAL_PREFIX ? a.us + (long long)p * N : nullptr;
+    const float* us  = (a.scal == SCAL_PREFIX || (a.scal == SCAL_SIGNED && a.us)) ? a.us + (long long)p * N : nullptr;
     for (int dir = 0; dir < (lap ? 2 : 1); dir++) {
         if (tid == 0) carry[0] = 0.0f;
         __syncthreads();
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
                 const int       j = dir ? N - 1 - (int)i : (int)i;
                 if (i < N) {
                     A[k] = lap ? (dir ? dec(j + 1) : dec(j)) : 1.0f;
-                    B[k] = lap ? 1.0f : (us ? us[isorted[j]] : xs[j]);
+                    B[k] = us ? us[isorted[j]] : (lap ? 1.0f : xs[j]);
                 } else { A[k] = 1.0f; B[k] = 0.0f; }
                 ca = A[k] * ca; cb = fmaf(A[k], cb, B[k]);
             }
@@ -240,6 +240,9 @@ __global__ void __launch_bounds__(256) rank_records(
         e1 = r < N ? expf(-(xs[r] - y)) : 0.0f;
         if (a.scal == SCAL_UNIT)
             atomicAdd(a.out_u + (long long)p * M + row, (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+        else if (a.scal == SCAL_SIGNED)
+            a.out_s[seg * M + row] = (a.uq ? a.uq[(long long)p * M + row] : 1.0f)
+                                   * ((r < N ? e1 * su1[r] : 0.0f) - (r > 0 ? e0 * su0[r - 1] : 0.0f));
     } else {
         if (a.mode == MODE_ABS) { e0 = 2.0f * y; e1 = a.rows_coef ? -2.0f : 0.0f; }
         if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + row, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));

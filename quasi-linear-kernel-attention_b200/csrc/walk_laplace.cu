@@ -1,6 +1,12 @@
 // Laplace walk: out[p, row_m, :] += e0_m * L_{r-1} + e1_m * R_r for every query m of every
 // segment, where r is the query's rank, L the decayed prefix sum of the gathered rows and R
 // the decayed suffix sum (recurrences of Weighted_Laplace_Sum/csrc/laplace_kernels.cu:5-13).
+// Two more emissions serve the gradients of the sum, which the reference does not have (its
+// training route is the chunked PyTorch path, Experiments/kernel_attention/attention.py:110-115):
+//   LAP_DOT   out_s[seg, row_m] += <g[p, row_m, :], e1_m * R_r - e0_m * L_{r-1}>   (d/dquery of the sum,
+//             contracted with the upstream gradient; one writer per element, added to the scalar
+//             term that the sort/rank kernel stored there)
+//   LAP_BOTH  the row reduction and the dot from one walk (grad_v and grad_k share stream and queries)
 //
 // Replaces the reference's laplace_chunk / laplace_scan / laplace_walk trio
 // (laplace_kernels.cu:65-127, 134-188, 219-409) with one persistent kernel:
@@ -23,15 +29,19 @@
 
 namespace qlka {
 
-template <int LPS, int CPL>
+enum { LAP_ROWS = 0, LAP_DOT = 1, LAP_BOTH = 2 };
+
+template <int LPS, int CPL, int EMIT>
 __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS : 1)) laplace_walk(const WalkArgs a)
 {
+    constexpr bool DO_ROWS = EMIT != LAP_DOT, DO_DOT = EMIT != LAP_ROWS;
     constexpr int STREAMS = WALK_THREADS / LPS;
     constexpr int CW      = LPS * CPL;               // channel capacity of a stream
     extern __shared__ __align__(16) float4 smem[];
     float4* ring  = smem;                                                    // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
     uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());   // [STREAMS][RING_DEPTH][LPS]
     float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);       // [STREAMS][RING_DEPTH][SX_STRIDE]
+    float4* g_area = reinterpret_cast<float4*>(sx_all + STREAMS * RING_DEPTH * SX_STRIDE);   // dot emissions only: [G_SLOTS][CPL/4][WALK_THREADS]
     // stream aggregates live in the ring's memory between the two passes
     float (*sF)[CW] = reinterpret_cast<float (*)[CW]>(ring);                 // forward aggregate  -> incoming prefix state
     float (*sB)[CW] = sF + STREAMS;                                          // backward aggregate -> incoming suffix state
@@ -54,6 +64,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
     f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
     f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = true;
+    f.g_s = smem_u32(g_area + tid);
 
     // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
@@ -71,7 +82,10 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
         f.rows   = a.rows + (long long)p * N * C4 + c0l;
         f.mstart = a.mstart + (long long)sg * mstride(N);
         f.yrec   = a.yrec + (long long)sg * (M + 1);
-        float*          out  = a.out + (long long)p * a.Mrows * C4 + c0l;
+        float*          out   = DO_ROWS ? a.out + (long long)p * a.Mrows * C4 + c0l : nullptr;
+        const float*    g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
+        float*          out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
+        f.grows = g;
         const long long slot = (long long)blockIdx.x * SEGS + sl;
         float*          ck   = a.ckpt + slot * NBK * C4 + c0l;
         float*          wk   = a.wck + slot * NBK;
@@ -166,7 +180,19 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
             int cur = 0;
             for (int t = 0; t < nblk; t++) {
                 const int b = b0 + t, j0 = b * KB;
-                __syncwarp(gmask);
+                float av[KB + 1];
+                uint32_t m_lo, m_hi, cnt;
+                if (DO_DOT) {
+                    // the block's copies have had a whole iteration; once its records are readable the emit-side rows
+                    // of its first G_SLOTS queries start, ahead of the next block's copies, and land during the arithmetic
+                    cp_async_wait<0>();
+                    __syncwarp(gmask);
+                    f.read_scalars(cur, av, m_lo, m_hi);
+                    cnt = m_hi - m_lo;
+                    f.issue_g(cur, 0u, cnt < (uint32_t)LPS ? min(cnt, (uint32_t)G_SLOTS) : 0u);
+                } else {
+                    __syncwarp(gmask);
+                }
 
                 // suffix state entering the block from above: corrected checkpoint, or the stream's incoming state
                 Vec<CPL> Rn;
@@ -178,12 +204,14 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 }
                 load_ckpt(b + 2);
 
-                f.step(t, cur, b0, 1, nblk);
-                __syncwarp(gmask);
-                float av[KB + 1];
-                uint32_t m_lo, m_hi;
-                f.read_scalars(cur, av, m_lo, m_hi);
-                const uint32_t cnt = m_hi - m_lo;
+                if (DO_DOT) {
+                    f.step_issue(t, cur, b0, 1, nblk);
+                } else {
+                    f.step(t, cur, b0, 1, nblk);
+                    __syncwarp(gmask);
+                    f.read_scalars(cur, av, m_lo, m_hi);
+                    cnt = m_hi - m_lo;
+                }
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
 
@@ -204,9 +232,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                     }
                 }
                 // the block's queries, in rank order
-                auto emit = [&](const uint4 rec, const Vec<CPL>& Lq, const Vec<CPL>& Rq) {
+                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record (row 0 for the sentinel)
+                    const float* gr = g + (size_t)rec.z * C4;
+                    #pragma unroll
+                    for (int c = 0; c < CPL; c += 4) {
+                        const float4 t4 = lane_on ? ldg4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        gq.x[c] = t4.x; gq.x[c + 1] = t4.y; gq.x[c + 2] = t4.z; gq.x[c + 3] = t4.w;
+                    }
+                };
+                auto emit_rows = [&](const uint4 rec, const Vec<CPL>& Lq, const Vec<CPL>& Rq) {
                     const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
-                    if (on) {
+                    if (DO_ROWS && on) {
                         float* o = out + (size_t)rec.z * C4;
                         #pragma unroll
                         for (int c = 0; c < CPL; c += 4)
@@ -217,17 +253,49 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                                      fmaf(e0, Lq.x[c + 3], e1 * Rq.x[c + 3]));
                     }
                 };
+                auto dot_part = [&](const uint4 rec, const Vec<CPL>& Lq, const Vec<CPL>& Rq, const Vec<CPL>& gq) -> float {
+                    const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
+                    float acc = 0.0f;
+                    #pragma unroll
+                    for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(e1, Rq.x[c], -e0 * Lq.x[c]), acc);
+                    return acc;
+                };
+                if (DO_DOT) {
+                    cp_async_wait<1>();               // the emit-side rows are in; the next block's copies may still fly
+                    __syncwarp(gmask);                // every lane has its rows in registers: the slot may hold partial dots
+                }
                 if (cnt < (uint32_t)LPS) {
                     // usual case: every record of the block and a closing sentinel sit in the staged slot
                     uint32_t qa  = f.qs_s + cur * LPS * 16;
                     uint4    rec = lds128u(qa);
+                    uint32_t n = 0, nb = min(cnt, (uint32_t)G_SLOTS);      // records [0, nb) have their emit-side rows staged
                     #pragma unroll
                     for (int i = 0; i < KB; i++) {
                         while (rec.w == (uint32_t)(j0 + i)) {
                             qa += 16;
                             const uint4 nxt = lds128u(qa);
-                            emit(rec, v[i], Rb[i]);
+                            emit_rows(rec, v[i], Rb[i]);
+                            if (DO_DOT) {
+                                if (n == nb) {                 // a block with more queries than slots: the next batch
+                                    const uint32_t n1 = min(cnt, nb + (uint32_t)G_SLOTS);
+                                    f.issue_g(cur, nb, n1);
+                                    cp_async_wait<0>();
+                                    nb = n1;
+                                }
+                                Vec<CPL> gq;
+                                gq.zero();
+                                if (lane_on) f.read_g(n, gq);
+                                f.put_part(cur, n, dot_part(rec, v[i], Rb[i], gq));
+                            }
                             rec = nxt;
+                            ++n;
+                        }
+                    }
+                    if (DO_DOT) {
+                        __syncwarp(gmask);
+                        if ((uint32_t)ln < cnt) {             // lane n finishes query n of the block
+                            const float sum = f.sum_parts(cur, (uint32_t)ln);
+                            atomicAdd(out_s + lds32u(f.qs_s + (cur * LPS + ln) * 16 + 8), sum);
                         }
                     }
                 } else {
@@ -240,7 +308,15 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                         while (n < cnt && rec.w == (uint32_t)(j0 + i)) {
                             ++n;
                             const uint4 nxt = __ldg(yp + n);        // at most the segment's sentinel
-                            emit(rec, v[i], Rb[i]);
+                            emit_rows(rec, v[i], Rb[i]);
+                            if (DO_DOT) {
+                                Vec<CPL> gq;
+                                load_g(rec, gq);
+                                float acc = dot_part(rec, v[i], Rb[i], gq);
+                                #pragma unroll
+                                for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
+                                if (ln == 0) atomicAdd(out_s + rec.z, acc);
+                            }
                             rec = nxt;
                         }
                     }
@@ -252,24 +328,33 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
     }
 }
 
-template <int LPS, int CPL>
+template <int LPS, int CPL, int EMIT>
 static cudaError_t launch_lap(const WalkArgs& a, int grid, cudaStream_t stream) {
-    auto kern = laplace_walk<LPS, CPL>;
-    const size_t smem = walk_smem_bytes<LPS, CPL>();
+    auto kern = laplace_walk<LPS, CPL, EMIT>;
+    const size_t smem = walk_smem_bytes<LPS, CPL>() + (EMIT != LAP_ROWS ? g_area_bytes<CPL>() : 0);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<grid, WALK_THREADS, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
+template <int EMIT>
+static cudaError_t launch_lap_c(const WalkArgs& a, int grid, cudaStream_t stream) {
+    if (a.C4 <= 32)  return launch_lap<8, 4, EMIT>(a, grid, stream);
+    if (a.C4 <= 64)  return launch_lap<16, 4, EMIT>(a, grid, stream);
+    if (a.C4 <= 128) return launch_lap<16, 8, EMIT>(a, grid, stream);
+    return cudaErrorInvalidValue;
+}
+
 // lanes per stream for a padded channel count
 int walk_lanes_per_stream(int C4) { return C4 <= 32 ? 8 : 16; }
 int walk_threads() { return WALK_THREADS; }
 
-cudaError_t launch_laplace_walk(const WalkArgs& a, int grid, cudaStream_t stream) {
-    if (a.C4 <= 32)  return launch_lap<8, 4>(a, grid, stream);
-    if (a.C4 <= 64)  return launch_lap<16, 4>(a, grid, stream);
-    if (a.C4 <= 128) return launch_lap<16, 8>(a, grid, stream);
+// emit: 0 = row reductions (the forward sum), 1 = dot, 2 = both
+cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream) {
+    if (emit == LAP_ROWS) return launch_lap_c<LAP_ROWS>(a, grid, stream);
+    if (emit == LAP_DOT)  return launch_lap_c<LAP_DOT>(a, grid, stream);
+    if (emit == LAP_BOTH) return launch_lap_c<LAP_BOTH>(a, grid, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -32,6 +32,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
     float4* ring   = smem;
     uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
     float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);
+    float4* g_area = reinterpret_cast<float4*>(sx_all + STREAMS * RING_DEPTH * SX_STRIDE);     // dot emissions only
     float (*sV)[CW] = reinterpret_cast<float (*)[CW]>(ring);     // stream sums, in the ring's memory between the passes
     float (*sK)[CW] = sV + STREAMS;
 
@@ -50,6 +51,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
     f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
     f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = WITH_K;
+    f.g_s = smem_u32(g_area + tid);
 
     // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
@@ -138,6 +140,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
         float*       out   = DO_ROWS ? a.out + (long long)p * a.Mrows * C4 + c0l : nullptr;
         const float* g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
         float*       out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
+        f.grows = g;
 
         // ---------------- pass 2: forward with emission
         {
@@ -146,13 +149,24 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
             int cur = 0;
             for (int t = 0; t < nblk; t++) {
                 const int b = b0 + t, j0 = b * KB;
-                __syncwarp(gmask);
-                f.step(t, cur, b0, 1, nblk);
-                __syncwarp(gmask);
                 float kv[KB + 1];
-                uint32_t m_lo, m_hi;
-                f.read_scalars(cur, kv, m_lo, m_hi);      // (the key values are only staged and used by EMIT_ROWS)
-                const uint32_t cnt = m_hi - m_lo;
+                uint32_t m_lo, m_hi, cnt;
+                if (DO_DOT) {
+                    // the block's copies have had a whole iteration; once its records are readable the emit-side rows
+                    // of its first G_SLOTS queries start, ahead of the next block's copies, and land during the arithmetic
+                    cp_async_wait<0>();
+                    __syncwarp(gmask);
+                    f.read_scalars(cur, kv, m_lo, m_hi);
+                    cnt = m_hi - m_lo;
+                    f.issue_g(cur, 0u, cnt < (uint32_t)LPS ? min(cnt, (uint32_t)G_SLOTS) : 0u);
+                    f.step_issue(t, cur, b0, 1, nblk);
+                } else {
+                    __syncwarp(gmask);
+                    f.step(t, cur, b0, 1, nblk);
+                    __syncwarp(gmask);
+                    f.read_scalars(cur, kv, m_lo, m_hi);      // (the key values are only staged and used by EMIT_ROWS)
+                    cnt = m_hi - m_lo;
+                }
                 Vec<CPL> v[KB], kb[WITH_K ? KB : 1];
                 f.read_rows(cur, j0, v);
                 // prefix states before each key, in place of the rows
@@ -174,7 +188,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                         gq.x[c] = t4.x; gq.x[c + 1] = t4.y; gq.x[c + 2] = t4.z; gq.x[c + 3] = t4.w;
                     }
                 };
-                auto emit = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq, const Vec<CPL>& gq) {
+                auto emit_rows = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq) {
                     if (DO_ROWS) {
                         const float e0 = __uint_as_float(rec.x);
                         const float ek = EMIT == EMIT_ROWS ? __uint_as_float(rec.y) : -2.0f;     // (rec.y is the dot term's addend in EMIT_BOTH)
@@ -189,30 +203,49 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                                          fmaf(e0, Pq.x[c + 3], ek * Kq.x[c + 3]));
                         }
                     }
-                    if (DO_DOT) {
-                        float acc = 0.0f;
-                        #pragma unroll
-                        for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(2.0f, Pq.x[c], -wt.x[c]), acc);
-                        #pragma unroll
-                        for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
-                        if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
-                    }
                 };
+                auto dot_part = [&](const Vec<CPL>& Pq, const Vec<CPL>& gq) -> float {
+                    float acc = 0.0f;
+                    #pragma unroll
+                    for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(2.0f, Pq.x[c], -wt.x[c]), acc);
+                    return acc;
+                };
+                if (DO_DOT) {
+                    cp_async_wait<1>();               // the emit-side rows are in; the next block's copies may still fly
+                    __syncwarp(gmask);                // every lane has its rows in registers: the slot may hold partial dots
+                }
                 if (cnt < (uint32_t)LPS) {
                     uint32_t qa  = f.qs_s + cur * LPS * 16;
                     uint4    rec = lds128u(qa);
-                    Vec<CPL> gq, gn;                  // emit-side rows are fetched one record ahead
-                    gn.zero();
-                    if (DO_DOT) load_g(rec, gn);
+                    uint32_t n = 0, nb = min(cnt, (uint32_t)G_SLOTS);      // records [0, nb) have their emit-side rows staged
                     #pragma unroll
                     for (int i = 0; i < KB; i++) {
                         while (rec.w == (uint32_t)(j0 + i)) {
                             qa += 16;
                             const uint4 nxt = lds128u(qa);
-                            gq = gn;
-                            if (DO_DOT) load_g(nxt, gn);
-                            emit(rec, v[i], kb[WITH_K ? i : 0], gq);
+                            emit_rows(rec, v[i], kb[WITH_K ? i : 0]);
+                            if (DO_DOT) {
+                                if (n == nb) {                 // a block with more queries than slots: the next batch
+                                    const uint32_t n1 = min(cnt, nb + (uint32_t)G_SLOTS);
+                                    f.issue_g(cur, nb, n1);
+                                    cp_async_wait<0>();
+                                    nb = n1;
+                                }
+                                Vec<CPL> gq;
+                                gq.zero();
+                                if (lane_on) f.read_g(n, gq);
+                                f.put_part(cur, n, dot_part(v[i], gq));
+                            }
                             rec = nxt;
+                            ++n;
+                        }
+                    }
+                    if (DO_DOT) {
+                        __syncwarp(gmask);
+                        if ((uint32_t)ln < cnt) {             // lane n finishes query n of the block
+                            const float sum = f.sum_parts(cur, (uint32_t)ln);
+                            const uint4 r   = lds128u(f.qs_s + (cur * LPS + ln) * 16);
+                            out_s[r.z] = a.sign * (sum + __uint_as_float(r.y));
                         }
                     }
                 } else {
@@ -224,10 +257,15 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                         while (n < cnt && rec.w == (uint32_t)(j0 + i)) {
                             ++n;
                             const uint4 nxt = __ldg(yp + n);
-                            Vec<CPL> gq;
-                            gq.zero();
-                            if (DO_DOT) load_g(rec, gq);
-                            emit(rec, v[i], kb[WITH_K ? i : 0], gq);
+                            emit_rows(rec, v[i], kb[WITH_K ? i : 0]);
+                            if (DO_DOT) {
+                                Vec<CPL> gq;
+                                load_g(rec, gq);
+                                float acc = dot_part(v[i], gq);
+                                #pragma unroll
+                                for (int off = LPS / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(gmask, acc, off);
+                                if (ln == 0) out_s[rec.z] = a.sign * (acc + __uint_as_float(rec.y));
+                            }
                             rec = nxt;
                         }
                     }
@@ -242,7 +280,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
 template <int LPS, int CPL, int EMIT>
 static cudaError_t launch_pw(const WalkArgs& a, int grid, cudaStream_t stream) {
     auto kern = prefix_walk<LPS, CPL, EMIT>;
-    const size_t smem = walk_smem_bytes<LPS, CPL>();
+    const size_t smem = walk_smem_bytes<LPS, CPL>() + (EMIT != EMIT_ROWS ? g_area_bytes<CPL>() : 0);
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<grid, WALK_THREADS, smem, stream>>>(a);

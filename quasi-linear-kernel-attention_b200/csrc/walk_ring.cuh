@@ -12,6 +12,18 @@
 // adds the block's query range [m_lo, m_hi). All of these are read by every lane of the stream
 // after a sub-warp barrier; a sub-warp barrier at the top of the next iteration lets the slot
 // be refilled. Shared memory is addressed with 32-bit shared-window addresses throughout.
+//
+// Walks that contract their state with a row of a second matrix per query (the dot emissions)
+// need that row, whose index is only known once the query's record has arrived. Fetching it when
+// the record is emitted puts one L2 round trip on every query of a stream; instead each thread
+// copies its slice of the rows of up to G_SLOTS of the block's queries into a private third area
+// as soon as the block's records are readable, and emits after the block's arithmetic.
+//
+// The dot of a query is a sum over the lanes of its stream. Warp shuffles inside the emission loop
+// would split a warp that carries two or four streams (their loops have different trip counts) for good,
+// so each lane parks its partial sum in shared memory - in the stream's part of the row slot in use,
+// whose rows are in registers by then - and after the loop lane n adds up the partials of query n and
+// writes the result: no shuffle, one writer per query, and the writes of a block go out together.
 #pragma once
 #include "qlka_common.cuh"
 
@@ -30,6 +42,7 @@ constexpr int WALK_THREADS = QLKA_WALK_THREADS;
 constexpr int RING_DEPTH   = QLKA_RING_DEPTH;   // blocks in flight: the one in use and RING_DEPTH - 1 prefetched
 constexpr int RING_AHEAD   = RING_DEPTH - 1;
 constexpr int SX_STRIDE    = 12;     // floats per staged scalar slot: 8 decays / keys, the next one, pad, m_lo, m_hi
+constexpr int G_SLOTS      = 8;      // emit-side rows staged per batch (a power of two)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -47,6 +60,19 @@ __device__ __forceinline__ float4 lds128(const uint32_t addr) {
     float4 v;
     asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
+}
+__device__ __forceinline__ uint32_t lds32u(const uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds32f(const uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts32f(const uint32_t addr, const float v) {
+    asm volatile("st.shared.f32 [%0], %1;" :: "r"(addr), "f"(v) : "memory");
 }
 __device__ __forceinline__ uint4 lds128u(const uint32_t addr) {
     uint4 v;
@@ -76,6 +102,8 @@ template <int LPS, int CPL> __host__ __device__ constexpr size_t walk_smem_bytes
     return ring_bytes<CPL>() + (size_t)(WALK_THREADS / LPS) * RING_DEPTH * LPS * sizeof(uint4)
          + (size_t)(WALK_THREADS / LPS) * RING_DEPTH * SX_STRIDE * sizeof(float);
 }
+// the emit-side row area of the dot emissions follows: [G_SLOTS][CPL/4][WALK_THREADS] x 16 B
+template <int CPL> __host__ __device__ constexpr size_t g_area_bytes() { return (size_t)G_SLOTS * (CPL / 4) * WALK_THREADS * 16; }
 
 // what one stream needs to stage its blocks
 template <int LPS, int CPL>
@@ -91,6 +119,8 @@ struct Feeder {
     uint32_t        row_bytes; // C4 * 4
     int             N, ln;
     bool            with_x, with_q;
+    uint32_t        g_s;       // dot emissions: shared address of this thread's float4 in emit-side slot 0
+    const float*    grows;     //                + p*M*C4 + lane channel offset
     // prefetched one block before its issue
     uint4    p0, p1;
     uint32_t ms0, ms1;
@@ -151,11 +181,54 @@ struct Feeder {
         }
         if (RING_AHEAD < nblk) prefetch_index(bfirst + dir * RING_AHEAD);
     }
-    __device__ __forceinline__ void step(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
+    __device__ __forceinline__ void step_issue(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
         if (t + RING_AHEAD < nblk) issue(cur == 0 ? RING_DEPTH - 1 : cur - 1, bfirst + dir * (t + RING_AHEAD));
         else cp_async_commit();
         if (t + RING_AHEAD + 1 < nblk) prefetch_index(bfirst + dir * (t + RING_AHEAD + 1));
+    }
+    __device__ __forceinline__ void step(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
+        step_issue(t, cur, bfirst, dir, nblk);
         cp_async_wait<RING_AHEAD>();
+    }
+
+    // start the copies of this thread's slice of the emit-side rows of the staged records n0 .. n1-1 of `slot`
+    // (n1 - n0 <= G_SLOTS; record n lands in emit-side slot n mod G_SLOTS); one commit group
+    __device__ __forceinline__ void issue_g(const int slot, const uint32_t n0, const uint32_t n1) {
+        const char* gb = reinterpret_cast<const char*>(grows);
+        #pragma unroll
+        for (int i = 0; i < G_SLOTS; i++) {
+            const uint32_t n = n0 + i;
+            if (n < n1) {
+                const uint32_t row = lds32u(qs_s + (slot * LPS + n) * 16 + 8);
+                const char*    src = gb + (size_t)row * row_bytes;
+                #pragma unroll
+                for (int h = 0; h < CPL / 4; h++)
+                    cp_async16(g_s + ((n & (G_SLOTS - 1)) * (CPL / 4) + h) * WALK_THREADS * 16, src + 16 * h);
+            }
+        }
+        cp_async_commit();
+    }
+    // Partial dots of query n of the block in `slot`: LPS floats inside the stream's share (LPS x 16 bytes) of row
+    // (n mod 8) of the slot, at a word offset that puts the LPS lanes' reads of LPS different queries in different banks.
+    __device__ __forceinline__ uint32_t part_addr(const int slot, const uint32_t n) const {
+        return ring_s - ln * 16 + slot * ring_slot_bytes<CPL>() + (n & 7u) * (WALK_THREADS * 16) + ((n >> 3) * 32u + n) * 4u;
+    }
+    __device__ __forceinline__ void put_part(const int slot, const uint32_t n, const float acc) const {
+        sts32f(part_addr(slot, n) + ln * 4, acc);
+    }
+    __device__ __forceinline__ float sum_parts(const int slot, const uint32_t n) const {
+        const uint32_t p = part_addr(slot, n);
+        float s0 = 0.0f, s1 = 0.0f;
+        #pragma unroll
+        for (int k = 0; k < LPS; k += 2) { s0 += lds32f(p + 4 * k); s1 += lds32f(p + 4 * k + 4); }
+        return s0 + s1;
+    }
+    __device__ __forceinline__ void read_g(const uint32_t n, Vec<CPL>& gq) const {
+        #pragma unroll
+        for (int h = 0; h < CPL / 4; h++) {
+            const float4 t = lds128(g_s + ((n & (G_SLOTS - 1)) * (CPL / 4) + h) * WALK_THREADS * 16);
+            gq.x[4 * h] = t.x; gq.x[4 * h + 1] = t.y; gq.x[4 * h + 2] = t.z; gq.x[4 * h + 3] = t.w;
+        }
     }
 
     // this thread's slice of the block's rows from `slot`; rows at positions >= N read as zero

@@ -31,13 +31,15 @@ def lib():
         L.qlka_status_string.restype = ctypes.c_char_p
         L.qlka_status_string.argtypes = [_i]
         L.qlka_last_cuda_error.restype = _i
-        for name in ("laplace_forward", "abs_forward", "abs_backward", "sgn_forward"):
+        for name in ("laplace_forward", "laplace_backward", "abs_forward", "abs_backward", "sgn_forward"):
             f = getattr(L, f"qlka_{name}_workspace_bytes")
             f.restype, f.argtypes = _i, [_i] * 5 + [ctypes.POINTER(_sz)]
         L.qlka_sort_rank_workspace_bytes.restype = _i
         L.qlka_sort_rank_workspace_bytes.argtypes = [_i] * 4 + [ctypes.POINTER(_sz)]
         L.qlka_weighted_laplace_sum_forward.restype = _i
         L.qlka_weighted_laplace_sum_forward.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp]
+        L.qlka_weighted_laplace_sum_backward.restype = _i
+        L.qlka_weighted_laplace_sum_backward.argtypes = [_vp] * 8 + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_laplace_forward_stage_ms.restype = _i
         L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 2
         L.qlka_noalloc_scratch_bytes.restype = _sz
@@ -279,6 +281,27 @@ def abs_backward(q, k, v, g_w, g_u=None):
                                               None if g_u is None else g_u.data_ptr(),
                                               gq.data_ptr(), gk.data_ptr(), gv.data_ptr(),
                                               ws.data_ptr(), n, P, D, N, M, C, _stream())
+    if st:
+        _raise(st)
+    return gq, gk, gv
+
+
+def laplace_backward(q, k, v, g_w, g_u=None):
+    """Gradients (grad_q, grad_k, grad_v) of sum(out_w * g_w) + sum(out_u * g_u) of the Laplace sum."""
+    P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
+    _check_like(g_w, "g_w", (P, M, C), q)
+    if g_u is not None:
+        _check_like(g_u, "g_u", (P, M), q)
+    L = lib()
+    with torch.cuda.device(q.device):
+        ws, n = _workspace(L.qlka_laplace_backward_workspace_bytes, dims, q.device)
+        gq = torch.empty(P, D, M, dtype=torch.float32, device=q.device)
+        gk = torch.empty(P, D, N, dtype=torch.float32, device=q.device)
+        gv = torch.empty(P, N, C, dtype=torch.float32, device=q.device)
+        st = L.qlka_weighted_laplace_sum_backward(q.data_ptr(), k.data_ptr(), v.data_ptr(), g_w.data_ptr(),
+                                                  None if g_u is None else g_u.data_ptr(),
+                                                  gq.data_ptr(), gk.data_ptr(), gv.data_ptr(),
+                                                  ws.data_ptr(), n, P, D, N, M, C, _stream())
     if st:
         _raise(st)
     return gq, gk, gv

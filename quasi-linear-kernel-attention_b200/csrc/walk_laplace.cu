@@ -112,9 +112,9 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 #pragma unroll
                 for (int i = KB - 1; i >= 0; i--) {
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) {
-                        F.x[c]  = fmaf(w, v[i].x[c], F.x[c]);
-                        Rl.x[c] = fmaf(av[i + 1], Rl.x[c], v[i].x[c]);
+                    for (int c = 0; c < CPL; c += 2) {
+                        fma2(F.x[c], F.x[c + 1], w, w, v[i].x[c], v[i].x[c + 1], F.x[c], F.x[c + 1]);
+                        fma2(Rl.x[c], Rl.x[c + 1], av[i + 1], av[i + 1], Rl.x[c], Rl.x[c + 1], v[i].x[c], v[i].x[c + 1]);
                     }
                     wprev = w;
                     w *= av[i];
@@ -219,16 +219,19 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 #pragma unroll
                 for (int i = KB - 1; i >= 0; i--) {
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) { Rn.x[c] = fmaf(av[i + 1], Rn.x[c], v[i].x[c]); Rb[i].x[c] = Rn.x[c]; }
+                    for (int c = 0; c < CPL; c += 2) {
+                        fma2(Rn.x[c], Rn.x[c + 1], av[i + 1], av[i + 1], Rn.x[c], Rn.x[c + 1], v[i].x[c], v[i].x[c + 1]);
+                        Rb[i].x[c] = Rn.x[c]; Rb[i].x[c + 1] = Rn.x[c + 1];
+                    }
                 }
                 // prefix state before each key, in place of the rows
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) {
-                        const float t2 = v[i].x[c];
-                        v[i].x[c] = L.x[c];
-                        L.x[c] = fmaf(av[i], L.x[c], t2);
+                    for (int c = 0; c < CPL; c += 2) {
+                        const float t0 = v[i].x[c], t1 = v[i].x[c + 1];
+                        v[i].x[c] = L.x[c]; v[i].x[c + 1] = L.x[c + 1];
+                        fma2(L.x[c], L.x[c + 1], av[i], av[i], L.x[c], L.x[c + 1], t0, t1);
                     }
                 }
                 // the block's queries, in rank order
@@ -245,20 +248,27 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                     if (DO_ROWS && on) {
                         float* o = out + (size_t)rec.z * C4;
                         #pragma unroll
-                        for (int c = 0; c < CPL; c += 4)
-                            red_add4(o + c,
-                                     fmaf(e0, Lq.x[c],     e1 * Rq.x[c]),
-                                     fmaf(e0, Lq.x[c + 1], e1 * Rq.x[c + 1]),
-                                     fmaf(e0, Lq.x[c + 2], e1 * Rq.x[c + 2]),
-                                     fmaf(e0, Lq.x[c + 3], e1 * Rq.x[c + 3]));
+                        for (int c = 0; c < CPL; c += 4) {
+                            float r0, r1, r2, r3;
+                            mul2(r0, r1, e1, e1, Rq.x[c], Rq.x[c + 1]);
+                            mul2(r2, r3, e1, e1, Rq.x[c + 2], Rq.x[c + 3]);
+                            fma2(r0, r1, e0, e0, Lq.x[c], Lq.x[c + 1], r0, r1);
+                            fma2(r2, r3, e0, e0, Lq.x[c + 2], Lq.x[c + 3], r2, r3);
+                            red_add4(o + c, r0, r1, r2, r3);
+                        }
                     }
                 };
                 auto dot_part = [&](const uint4 rec, const Vec<CPL>& Lq, const Vec<CPL>& Rq, const Vec<CPL>& gq) -> float {
                     const float e0 = __uint_as_float(rec.x), e1 = __uint_as_float(rec.y);
-                    float acc = 0.0f;
+                    float a0 = 0.0f, a1 = 0.0f;
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(e1, Rq.x[c], -e0 * Lq.x[c]), acc);
-                    return acc;
+                    for (int c = 0; c < CPL; c += 2) {
+                        float t0, t1;
+                        mul2(t0, t1, -e0, -e0, Lq.x[c], Lq.x[c + 1]);
+                        fma2(t0, t1, e1, e1, Rq.x[c], Rq.x[c + 1], t0, t1);
+                        fma2(a0, a1, gq.x[c], gq.x[c + 1], t0, t1, a0, a1);
+                    }
+                    return a0 + a1;
                 };
                 if (DO_DOT) {
                     cp_async_wait<1>();               // the emit-side rows are in; the next block's copies may still fly

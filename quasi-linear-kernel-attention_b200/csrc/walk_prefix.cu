@@ -93,9 +93,9 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) {
-                        PV.x[c] += v[i].x[c];
-                        if (WITH_K) PK.x[c] = fmaf(kv[i], v[i].x[c], PK.x[c]);
+                    for (int c = 0; c < CPL; c += 2) {
+                        add2(PV.x[c], PV.x[c + 1], PV.x[c], PV.x[c + 1], v[i].x[c], v[i].x[c + 1]);
+                        if (WITH_K) fma2(PK.x[c], PK.x[c + 1], kv[i], kv[i], v[i].x[c], v[i].x[c + 1], PK.x[c], PK.x[c + 1]);
                     }
                 }
                 cur = ring_next(cur);
@@ -173,11 +173,14 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 #pragma unroll
                 for (int i = 0; i < KB; i++) {
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) {
-                        const float t2 = v[i].x[c];
-                        v[i].x[c] = PV.x[c];
-                        PV.x[c] += t2;
-                        if (WITH_K) { kb[i].x[c] = PK.x[c]; PK.x[c] = fmaf(kv[i], t2, PK.x[c]); }
+                    for (int c = 0; c < CPL; c += 2) {
+                        const float t0 = v[i].x[c], t1 = v[i].x[c + 1];
+                        v[i].x[c] = PV.x[c]; v[i].x[c + 1] = PV.x[c + 1];
+                        add2(PV.x[c], PV.x[c + 1], PV.x[c], PV.x[c + 1], t0, t1);
+                        if (WITH_K) {
+                            kb[i].x[c] = PK.x[c]; kb[i].x[c + 1] = PK.x[c + 1];
+                            fma2(PK.x[c], PK.x[c + 1], kv[i], kv[i], t0, t1, PK.x[c], PK.x[c + 1]);
+                        }
                     }
                 }
                 auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record (row 0 for the sentinel)
@@ -195,20 +198,26 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                         if (on) {
                             float* o = out + (size_t)rec.z * C4;
                             #pragma unroll
-                            for (int c = 0; c < CPL; c += 4)
-                                red_add4(o + c,
-                                         fmaf(e0, Pq.x[c],     ek * Kq.x[c]),
-                                         fmaf(e0, Pq.x[c + 1], ek * Kq.x[c + 1]),
-                                         fmaf(e0, Pq.x[c + 2], ek * Kq.x[c + 2]),
-                                         fmaf(e0, Pq.x[c + 3], ek * Kq.x[c + 3]));
+                            for (int c = 0; c < CPL; c += 4) {
+                                float r0, r1, r2, r3;
+                                mul2(r0, r1, ek, ek, Kq.x[c], Kq.x[c + 1]);
+                                mul2(r2, r3, ek, ek, Kq.x[c + 2], Kq.x[c + 3]);
+                                fma2(r0, r1, e0, e0, Pq.x[c], Pq.x[c + 1], r0, r1);
+                                fma2(r2, r3, e0, e0, Pq.x[c + 2], Pq.x[c + 3], r2, r3);
+                                red_add4(o + c, r0, r1, r2, r3);
+                            }
                         }
                     }
                 };
                 auto dot_part = [&](const Vec<CPL>& Pq, const Vec<CPL>& gq) -> float {
-                    float acc = 0.0f;
+                    float a0 = 0.0f, a1 = 0.0f;
                     #pragma unroll
-                    for (int c = 0; c < CPL; c++) acc = fmaf(gq.x[c], fmaf(2.0f, Pq.x[c], -wt.x[c]), acc);
-                    return acc;
+                    for (int c = 0; c < CPL; c += 2) {
+                        float t0, t1;
+                        fma2(t0, t1, 2.0f, 2.0f, Pq.x[c], Pq.x[c + 1], -wt.x[c], -wt.x[c + 1]);
+                        fma2(a0, a1, gq.x[c], gq.x[c + 1], t0, t1, a0, a1);
+                    }
+                    return a0 + a1;
                 };
                 if (DO_DOT) {
                     cp_async_wait<1>();               // the emit-side rows are in; the next block's copies may still fly

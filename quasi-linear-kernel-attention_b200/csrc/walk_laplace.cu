@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
     f.ring_s = smem_u32(ring + tid);
     f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
-    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.ln = ln; f.with_x = true;
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = M; f.ln = ln; f.with_x = true;
     f.g_s = smem_u32(g_area + tid);
 
     // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
@@ -105,8 +105,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 f.step(t, cur, b1 - 1, -1, nblk);
                 __syncwarp(gmask);
                 float av[KB + 1];
-                uint32_t m_lo, m_hi;
-                f.read_scalars(cur, av, m_lo, m_hi);
+                f.read_scalars(cur, av);
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
                 #pragma unroll
@@ -181,14 +180,15 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
             for (int t = 0; t < nblk; t++) {
                 const int b = b0 + t, j0 = b * KB;
                 float av[KB + 1];
-                uint32_t m_lo, m_hi, cnt;
+                uint32_t cnt;
                 if (DO_DOT) {
                     // the block's copies have had a whole iteration; once its records are readable the emit-side rows
                     // of its first G_SLOTS queries start, ahead of the next block's copies, and land during the arithmetic
+                    f.advance_range();
                     cp_async_wait<0>();
                     __syncwarp(gmask);
-                    f.read_scalars(cur, av, m_lo, m_hi);
-                    cnt = m_hi - m_lo;
+                    f.read_scalars(cur, av);
+                    cnt = f.m_hi - f.m_lo;
                     f.issue_g(cur, 0u, cnt < (uint32_t)LPS ? min(cnt, (uint32_t)G_SLOTS) : 0u);
                 } else {
                     __syncwarp(gmask);
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                 } else {
                     f.step(t, cur, b0, 1, nblk);
                     __syncwarp(gmask);
-                    f.read_scalars(cur, av, m_lo, m_hi);
-                    cnt = m_hi - m_lo;
+                    f.read_scalars(cur, av);
+                    cnt = f.m_hi - f.m_lo;
                 }
                 Vec<CPL> v[KB];
                 f.read_rows(cur, j0, v);
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                     }
                 } else {
                     // more queries than the slot holds: read them from memory
-                    const uint4* yp  = f.yrec + m_lo;
+                    const uint4* yp  = f.yrec + f.m_lo;
                     uint32_t     n   = 0;
                     uint4        rec = __ldg(yp);
                     #pragma unroll

@@ -7,11 +7,12 @@
 // ever reads the rows it copied itself, so cp.async.wait_group is all the rows need.
 //
 // Per stream (LPS lanes) and slot, two more things ride in the same commit group: the block's
-// per-key scalars (9 floats, copied by lanes 0-2) and up to LPS - 1 query records of the block
-// (one 16-byte record per lane), closed by a sentinel record that a lane stores directly. Lane 3
-// adds the block's query range [m_lo, m_hi). All of these are read by every lane of the stream
-// after a sub-warp barrier; a sub-warp barrier at the top of the next iteration lets the slot
-// be refilled. Shared memory is addressed with 32-bit shared-window addresses throughout.
+// per-key scalars (12 floats of which 9 are used, copied by lanes 0-2) and the LPS query records
+// from the block's first one on (one 16-byte record per lane; a block with fewer than LPS
+// queries finds all of them there, followed by a record of a later block or the segment's
+// sentinel). Both are read by every lane of the stream after a sub-warp barrier; a sub-warp
+// barrier at the top of the next iteration lets the slot be refilled. The block's query range
+// travels in registers. Shared memory is addressed with 32-bit shared-window addresses throughout.
 //
 // Walks that contract their state with a row of a second matrix per query (the dot emissions)
 // need that row, whose index is only known once the query's record has arrived. Fetching it when
@@ -41,7 +42,7 @@ constexpr int WALK_THREADS = QLKA_WALK_THREADS;
 #endif
 constexpr int RING_DEPTH   = QLKA_RING_DEPTH;   // blocks in flight: the one in use and RING_DEPTH - 1 prefetched
 constexpr int RING_AHEAD   = RING_DEPTH - 1;
-constexpr int SX_STRIDE    = 12;     // floats per staged scalar slot: 8 decays / keys, the next one, pad, m_lo, m_hi
+constexpr int SX_STRIDE    = 12;     // floats per staged scalar slot: 8 decays / keys and the next four
 constexpr int G_SLOTS      = 8;      // emit-side rows staged per batch (a power of two)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -139,13 +140,15 @@ struct Feeder {
     const uint32_t* mstart;
     const uint4*    yrec;
     uint32_t        row_bytes; // C4 * 4
-    int             N, ln;
+    int             N, M, ln;
     bool            with_x, with_q;
     uint32_t        g_s;       // dot emissions: shared address of this thread's float4 in emit-side slot 0
     const float*    grows;     //                + p*M*C4 + lane channel offset
     // prefetched one block before its issue
     uint4    p0, p1;
     uint32_t ms0, ms1;
+    // query range [lo, hi) of the block in use and of the blocks in flight (all lanes load the same two words)
+    uint32_t m_lo, m_hi, mq_lo[RING_AHEAD], mq_hi[RING_AHEAD];
 
     __device__ __forceinline__ void prefetch_index(const int b) {
         p0 = __ldg(reinterpret_cast<const uint4*>(xperm + b * KB));
@@ -154,7 +157,8 @@ struct Feeder {
     }
 
     // start the copies of key block b (whose indices were prefetched) into `slot`; one commit group
-    __device__ __forceinline__ void issue(const int slot, const int b) {
+    __device__ __forceinline__ void issue(const int slot, const int b, const int ahead) {
+        mq_lo[ahead] = ms0; mq_hi[ahead] = ms1;
         const int      j0    = b * KB;
         const uint32_t pr[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
         const uint32_t dst   = ring_s + slot * ring_slot_bytes<CPL>();
@@ -177,18 +181,12 @@ struct Feeder {
             }
         }
         const uint32_t sx = sx_s + slot * SX_STRIDE * 4;
-        if (with_x) {
-            if (ln == 0)      cp_async16(sx, xval + j0);
-            else if (ln == 1) cp_async16(sx + 16, xval + j0 + 4);
-            else if (ln == 2) cp_async4(sx + 32, xval + j0 + 8);
-        }
+        if (with_x && ln < 3) cp_async16(sx + 16 * ln, xval + j0 + 4 * ln);       // (the array is padded by KB floats)
         if (with_q) {
-            // records 0 .. n-1 of the block, then a sentinel; n = min(count, LPS - 1)
-            const uint32_t n = min(ms1 - ms0, (uint32_t)(LPS - 1));
-            const uint32_t q = qs_s + (slot * LPS + ln) * 16;
-            if ((uint32_t)ln < n)       cp_async16(q, yrec + ms0 + ln);
-            else if ((uint32_t)ln == n) sts128u(q, make_uint4(0u, 0u, 0u, 0xffffffffu));
-            if (ln == 3) sts64u(sx + 40, ms0, ms1);
+            // the LPS records from the block's first on (clamped to the segment's sentinel): a block with fewer than
+            // LPS queries finds all of them here, followed by a record of a later block or the sentinel
+            const uint32_t r = min(ms0 + (uint32_t)ln, (uint32_t)M);
+            cp_async16(qs_s + (slot * LPS + ln) * 16, yrec + r);
         }
         cp_async_commit();
     }
@@ -198,17 +196,24 @@ struct Feeder {
     __device__ __forceinline__ void prologue(const int bfirst, const int dir, const int nblk) {
         #pragma unroll
         for (int s = 0; s < RING_AHEAD; s++) {
-            if (s < nblk) { prefetch_index(bfirst + dir * s); issue(s, bfirst + dir * s); }
+            if (s < nblk) { prefetch_index(bfirst + dir * s); issue(s, bfirst + dir * s, s); }
             else cp_async_commit();
         }
         if (RING_AHEAD < nblk) prefetch_index(bfirst + dir * RING_AHEAD);
     }
+    // first thing of every step: the oldest block in flight becomes the block in use
+    __device__ __forceinline__ void advance_range() {
+        m_lo = mq_lo[0]; m_hi = mq_hi[0];
+        #pragma unroll
+        for (int s = 0; s + 1 < RING_AHEAD; s++) { mq_lo[s] = mq_lo[s + 1]; mq_hi[s] = mq_hi[s + 1]; }
+    }
     __device__ __forceinline__ void step_issue(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
-        if (t + RING_AHEAD < nblk) issue(cur == 0 ? RING_DEPTH - 1 : cur - 1, bfirst + dir * (t + RING_AHEAD));
+        if (t + RING_AHEAD < nblk) issue(cur == 0 ? RING_DEPTH - 1 : cur - 1, bfirst + dir * (t + RING_AHEAD), RING_AHEAD - 1);
         else cp_async_commit();
         if (t + RING_AHEAD + 1 < nblk) prefetch_index(bfirst + dir * (t + RING_AHEAD + 1));
     }
     __device__ __forceinline__ void step(const int t, const int cur, const int bfirst, const int dir, const int nblk) {
+        advance_range();
         step_issue(t, cur, bfirst, dir, nblk);
         cp_async_wait<RING_AHEAD>();
     }
@@ -270,14 +275,13 @@ struct Feeder {
         }
     }
 
-    // the block's nine scalars and its query range, from `slot`
-    __device__ __forceinline__ void read_scalars(const int slot, float (&av)[KB + 1], uint32_t& m_lo, uint32_t& m_hi) const {
+    // the block's nine scalars, from `slot`
+    __device__ __forceinline__ void read_scalars(const int slot, float (&av)[KB + 1]) const {
         const uint32_t sx = sx_s + slot * SX_STRIDE * 4;
         const float4 a0 = lds128(sx), a1 = lds128(sx + 16), a2 = lds128(sx + 32);
         av[0] = a0.x; av[1] = a0.y; av[2] = a0.z; av[3] = a0.w;
         av[4] = a1.x; av[5] = a1.y; av[6] = a1.z; av[7] = a1.w;
         av[8] = a2.x;
-        m_lo = __float_as_uint(a2.z); m_hi = __float_as_uint(a2.w);
     }
 };
 

@@ -163,22 +163,11 @@ struct Feeder {
         const uint32_t pr[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
         const uint32_t dst   = ring_s + slot * ring_slot_bytes<CPL>();
         const char*    rb    = reinterpret_cast<const char*>(rows);
-        if (j0 + KB <= N) {
+        #pragma unroll
+        for (int i = 0; i < KB; i++) {                 // (positions past the last key point at row 0; read_rows zeroes them)
+            const char* src = rb + (size_t)pr[i] * row_bytes;
             #pragma unroll
-            for (int i = 0; i < KB; i++) {
-                const char* src = rb + (size_t)pr[i] * row_bytes;
-                #pragma unroll
-                for (int h = 0; h < CPL / 4; h++) cp_async16(dst + (i * (CPL / 4) + h) * WALK_THREADS * 16, src + 16 * h);
-            }
-        } else {
-            #pragma unroll
-            for (int i = 0; i < KB; i++) {
-                if (j0 + i < N) {
-                    const char* src = rb + (size_t)pr[i] * row_bytes;
-                    #pragma unroll
-                    for (int h = 0; h < CPL / 4; h++) cp_async16(dst + (i * (CPL / 4) + h) * WALK_THREADS * 16, src + 16 * h);
-                }
-            }
+            for (int h = 0; h < CPL / 4; h++) cp_async16(dst + (i * (CPL / 4) + h) * WALK_THREADS * 16, src + 16 * h);
         }
         const uint32_t sx = sx_s + slot * SX_STRIDE * 4;
         if (with_x && ln < 3) cp_async16(sx + 16 * ln, xval + j0 + 4 * ln);       // (the array is padded by KB floats)

@@ -101,6 +101,19 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
                                        void* workspace, size_t workspace_bytes,
                                        int P, int D, int N, int M, int C, qlka_stream_t stream);
 
+/* ---- add_laplace attention on the caller's layout ---------------------------------------
+ * out[b,h,i,:] = sum_j A_ij v[b,h,j,:] / max(sum_j A_ij, 1e-6),  A_ij = sum_d exp(-|q[b,h,i,d] - k[b,h,j,d]| / tau),
+ * with q, k (B, H, S, D), v and out (B, H, S, Dv) contiguous and keep (B, S) an optional key-keep mask of 0 / 1 floats
+ * (NULL: all keys kept). One call does what the reference spreads over attention() and _add_laplace
+ * (Experiments/kernel_attention/attention.py:67-72, 95-126) around its operator: the layout change to (P, D, S) fused
+ * with the division by tau and the zeroing of masked keys, the Laplace sum accumulated straight into `out`, and the
+ * normalisation with the row sum corrected for the masked keys. Forward only. `masked` in the size query is 1 when a
+ * keep mask will be passed. */
+int qlka_laplace_attention_workspace_bytes(int B, int H, int S, int D, int Dv, int masked, size_t* bytes);
+int qlka_laplace_attention_forward(const float* q, const float* k, const float* v, const float* keep /* nullable */,
+                                   float tau, float* out, void* workspace, size_t workspace_bytes,
+                                   int B, int H, int S, int D, int Dv, qlka_stream_t stream);
+
 /* ---- weighted abs sum, forward ---------------------------------------------------------
  * out_w[p,m,c] = sum_{d,n} |k[p,d,n] - q[p,d,m]| v[p,n,c]           (P, M, C)
  * out_u[p,m]   = sum_{d,n} |k[p,d,n] - q[p,d,m]|                    (P, M), optional (NULL)

@@ -103,6 +103,90 @@ __global__ void unpad_rows_kernel(const float* __restrict__ src, float* __restri
     dst[i] = src[r * C4 + c];
 }
 
+// ---- the caller's side of add_laplace attention (Experiments/kernel_attention/attention.py:67-72, 95-126) ----
+// dst[p, d, s] = src[p, s, d] * scale * (keep ? keep[p / H, s] : 1): the (B, H, S, D) -> (P, D, S) layout change of
+// attention(), the division by tau and the zeroing of masked keys in one pass; 32 x 32 tiles through shared memory
+__global__ void __launch_bounds__(256) transpose_scale_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                              const float* __restrict__ keep, const float scale,
+                                                              const int S, const int D, const int H)
+{
+    __shared__ float tile[32][33];
+    const int p  = blockIdx.z;
+    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
+    const float* sp = src + (long long)p * S * D;
+    float*       dp = dst + (long long)p * D * S;
+    #pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int s = s0 + r, d = d0 + tx;
+        float x = 0.0f;
+        if (s < S && d < D) {
+            x = sp[(long long)s * D + d] * scale;
+            if (keep) x *= keep[(long long)(p / H) * S + s];
+        }
+        tile[r][tx] = x;
+    }
+    __syncthreads();
+    #pragma unroll
+    for (int r = ty; r < 32; r += 8) {
+        const int d = d0 + r, s = s0 + tx;
+        if (d < D && s < S) dp[(long long)d * S + s] = tile[tx][r];
+    }
+}
+
+// dst[p, s, :] = src[p, s, :] * keep[p / H, s]
+__global__ void mask_rows_kernel(const float* __restrict__ src, float* __restrict__ dst, const float* __restrict__ keep,
+                                 const int S, const int C, const int H, const long long total)
+{
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long ps = i / C;
+    const long long p = ps / S, s = ps % S;
+    dst[i] = src[i] * keep[(p / H) * S + s];
+}
+
+// n_pad[b] = S - sum_s keep[b, s]; one CTA per b
+__global__ void __launch_bounds__(256) npad_kernel(const float* __restrict__ keep, float* __restrict__ n_pad, const int S) {
+    __shared__ float red[256];
+    const int b = blockIdx.x;
+    float acc = 0.0f;
+    for (int s = threadIdx.x; s < S; s += 256) acc += keep[(long long)b * S + s];
+    red[threadIdx.x] = acc;
+    __syncthreads();
+    for (int off = 128; off > 0; off >>= 1) {
+        if (threadIdx.x < off) red[threadIdx.x] += red[threadIdx.x + off];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) n_pad[b] = (float)S - red[0];
+}
+
+// out[p, m, :] /= max(out_u[p, m] - n_pad[p / H] * sum_d exp(-|qt[p, d, m]|), clamp): the row normalisation of
+// _add_laplace, with the row sum corrected for the masked keys (each sits at k = 0 with v = 0). One warp per row.
+__global__ void __launch_bounds__(256) laplace_normalise_kernel(float* __restrict__ out, const float* __restrict__ out_u,
+                                                                const float* __restrict__ qt, const float* __restrict__ n_pad,
+                                                                const int M, const int D, const int C, const int H,
+                                                                const float clamp, const long long rows)
+{
+    const long long row  = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int       lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const long long p = row / M, m = row % M;
+    float den = out_u[row];
+    if (n_pad) {
+        const float np = n_pad[p / H];
+        if (np != 0.0f) {
+            float acc = 0.0f;
+            for (int d = lane; d < D; d += 32) acc += __expf(-fabsf(qt[(p * D + d) * M + m]));
+            #pragma unroll
+            for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(FULL, acc, off);
+            den -= np * acc;
+        }
+    }
+    const float inv = 1.0f / fmaxf(den, clamp);
+    float* o = out + row * C;
+    for (int c = lane; c < C; c += 32) o[c] *= inv;
+}
+
 static inline unsigned blocks_for(long long total, int threads) { return (unsigned)((total + threads - 1) / threads); }
 
 cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st) {
@@ -133,6 +217,27 @@ cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C,
 cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st) {
     const long long total = rows * C;
     unpad_rows_kernel<<<blocks_for(total, 256), 256, 0, st>>>(src, dst, C, C4, total);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_transpose_scale(const float* src, float* dst, const float* keep, float scale, int P, int S, int D, int H, cudaStream_t st) {
+    dim3 grid((S + 31) / 32, (D + 31) / 32, P);
+    transpose_scale_kernel<<<grid, 256, 0, st>>>(src, dst, keep, scale, S, D, H);
+    return cudaGetLastError();
+}
+cudaError_t launch_mask_rows(const float* src, float* dst, const float* keep, int P, int S, int C, int H, cudaStream_t st) {
+    const long long total = (long long)P * S * C;
+    mask_rows_kernel<<<blocks_for(total, 256), 256, 0, st>>>(src, dst, keep, S, C, H, total);
+    return cudaGetLastError();
+}
+cudaError_t launch_npad(const float* keep, float* n_pad, int B, int S, cudaStream_t st) {
+    npad_kernel<<<B, 256, 0, st>>>(keep, n_pad, S);
+    return cudaGetLastError();
+}
+cudaError_t launch_laplace_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
+                                     int P, int M, int D, int C, int H, float clamp, cudaStream_t st) {
+    const long long rows = (long long)P * M;
+    laplace_normalise_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(out, out_u, qt, n_pad, M, D, C, H, clamp, rows);
     return cudaGetLastError();
 }
 

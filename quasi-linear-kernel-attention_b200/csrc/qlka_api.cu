@@ -22,6 +22,11 @@ cudaError_t launch_abs_init(const float* ktot, const float* vsum, const float* q
                             float* out, float* out_u, int P, int M, int C4, int Nk, float A, float Bq, cudaStream_t st);
 cudaError_t launch_pad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
 cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int C, int C4, cudaStream_t st);
+cudaError_t launch_transpose_scale(const float* src, float* dst, const float* keep, float scale, int P, int S, int D, int H, cudaStream_t st);
+cudaError_t launch_mask_rows(const float* src, float* dst, const float* keep, int P, int S, int C, int H, cudaStream_t st);
+cudaError_t launch_npad(const float* keep, float* n_pad, int B, int S, cudaStream_t st);
+cudaError_t launch_laplace_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
+                                     int P, int M, int D, int C, int H, float clamp, cudaStream_t st);
 }  // namespace qlka
 
 using namespace qlka;
@@ -373,6 +378,67 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
         CU(launch_laplace_walk(w, EMIT_BOTH, ws.plan_q.grid, stream));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
+    return QLKA_OK;
+}
+
+// ---------------------------------------------------------------- add_laplace attention on (B, H, S, D)
+namespace {
+struct LaplaceAttnWs {
+    float *qt, *kt, *vm, *out_u, *n_pad; void* inner; size_t inner_bytes, bytes;
+    LaplaceAttnWs(void* base, int B, int H, int S, int D, int C, bool masked) {
+        Bump b(base);
+        const size_t P = (size_t)B * H;
+        qt    = b.take<float>(P * D * S);
+        kt    = b.take<float>(P * D * S);
+        vm    = masked ? b.take<float>(P * S * C) : nullptr;
+        out_u = b.take<float>(P * S);
+        n_pad = masked ? b.take<float>((size_t)B) : nullptr;
+        inner_bytes = LaplaceWs(nullptr, (int)P, D, S, S, C).bytes;
+        inner = b.take<unsigned char>(inner_bytes);
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+}  // namespace
+
+static int attn_check(int B, int H, int S, int D, int C) {
+    if (B <= 0 || H <= 0) return QLKA_ERR_BAD_SHAPE;
+    if ((long long)B * H > 65535) return QLKA_ERR_UNSUPPORTED;
+    return check_dims(B * H, D, S, S, C);
+}
+
+int qlka_laplace_attention_workspace_bytes(int B, int H, int S, int D, int Dv, int masked, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = attn_check(B, H, S, D, Dv);
+    if (st) return st;
+    *bytes = LaplaceAttnWs(nullptr, B, H, S, D, Dv, masked != 0).bytes;
+    return QLKA_OK;
+}
+
+int qlka_laplace_attention_forward(const float* q, const float* k, const float* v, const float* keep, float tau,
+                                   float* out, void* workspace, size_t workspace_bytes,
+                                   int B, int H, int S, int D, int Dv, qlka_stream_t stream_)
+{
+    int st = attn_check(B, H, S, D, Dv);
+    if (st) return st;
+    if (!q || !k || !v || !out) return QLKA_ERR_NULL;
+    if (!(tau > 0.0f)) return QLKA_ERR_BAD_SHAPE;
+    const bool masked = keep != nullptr;
+    LaplaceAttnWs ws(workspace, B, H, S, D, Dv, masked);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int P = B * H;
+
+    CU(launch_transpose_scale(q, ws.qt, nullptr, 1.0f / tau, P, S, D, H, stream));
+    CU(launch_transpose_scale(k, ws.kt, keep, 1.0f / tau, P, S, D, H, stream));
+    const float* rows = v;
+    if (masked) {
+        CU(launch_mask_rows(v, ws.vm, keep, P, S, Dv, H, stream));
+        CU(launch_npad(keep, ws.n_pad, B, S, stream));
+        rows = ws.vm;
+    }
+    st = laplace_forward_impl(ws.qt, ws.kt, rows, out, ws.out_u, ws.inner, ws.inner_bytes, P, D, S, S, Dv, stream, nullptr);
+    if (st) return st;
+    CU(launch_laplace_normalise(out, ws.out_u, ws.qt, ws.n_pad, P, S, D, Dv, H, 1e-6f, stream));
     return QLKA_OK;
 }
 

@@ -12,6 +12,7 @@ reference (dense matrix kernels) are not part of this library.
 
 import torch
 
+import qlka_native as _native
 from weighted_abs_sum import weighted_abs_sum_full, weighted_abs_sum_shifted
 from weighted_laplace_sum import weighted_laplace_sum
 
@@ -66,6 +67,10 @@ def attention(q, k, v, kernel, tau, keep=None):
         raise ValueError(f"kernel must be one of {tuple(_KERNELS)}, got {kernel!r}")
     B, H, S, D = q.shape
     P = B * H
+    needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
+    if kernel == "add_laplace" and not needs_grad:
+        # inference: layout change, tau, masking, the sum and the normalisation in one native call
+        return _native.laplace_attention(q, k, v, tau, keep)
     q = q.transpose(2, 3).reshape(P, D, S)
     k = k.transpose(2, 3).reshape(P, D, S)
     v = v.reshape(P, S, v.shape[3])

@@ -117,3 +117,29 @@ def test_host_pipeline_matches_device_call():
         torch.cuda.synchronize()
         ref_w, ref_u = qlka_native.laplace_forward(q.cuda(), k.cuda(), v.cuda())
         assert rel_err(out_w_h, ref_w.double()) < 1e-5 and rel_err(out_u_h, ref_u.double()) < 1e-5
+
+
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("shape", [(1, 2, 50, 8, 8), (2, 3, 333, 16, 20), (1, 4, 1024, 32, 32), (2, 2, 700, 64, 33)])
+def test_fused_attention_entry(shape, masked):
+    """The one-call add_laplace attention on (B, H, S, D) against the float64 dense formula and the op-by-op route."""
+    import qlka_native
+    from kernel_attention import attention
+    B, H, S, D, Dv = shape
+    g = torch.Generator().manual_seed(S + D)
+    q, k = (torch.randn(B, H, S, D, generator=g).cuda() for _ in range(2))
+    v = torch.randn(B, H, S, Dv, generator=g).cuda()
+    keep = None
+    if masked:
+        keep = (torch.rand(B, S, generator=g) > 0.3)
+        keep[:, 0] = True
+        keep = keep.cuda()
+    out = qlka_native.laplace_attention(q, k, v, 0.5, keep)
+    ref = direct.attention(q, k, v, "add_laplace", 0.5, keep)
+    assert out.shape == (B, H, S, Dv)
+    assert rel_err(out, ref) < TOL, f"rel err {rel_err(out, ref)}"
+    assert rel_err(out, attention(q, k, v, "add_laplace", 0.5, keep).double()) < 1e-5     # same route without grad (atomics: order differs)
+    with torch.enable_grad():
+        qg = q.clone().requires_grad_(True)
+        slow = attention(qg, k, v, "add_laplace", 0.5, keep)                      # op-by-op route
+    assert rel_err(out, slow.double()) < 1e-5

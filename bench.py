@@ -168,7 +168,7 @@ def run_ours(args, rank, world, local_rank):
     n_e2e = max(2, min(args.steps, 5))
 
     # the host-buffer entry of the library: heads stream through copy / compute / copy-back in chunks
-    pipe = qlka_native.HostPipeline(P, D, N, N, C, chunk=max(1, P // 8), device=dev)
+    pipe = qlka_native.HostPipeline(P, D, N, N, C, chunk=max(1, P // 12), device=dev)      # (12 chunks measured best: 12.9 ms against 13.5 ms for 6)
 
     def e2e_step():
         pipe(q_h, k_h, v_h, out_w_h, out_u_h)
@@ -192,8 +192,8 @@ def run_ours(args, rank, world, local_rank):
     # dominant kernel: the walk (60 % of the device time, profiles/); its launch time is measured live
     achieved = ALGO_BYTES / (stage["walk_ms"] * 1e-3) / 1e9
     # DRAM traffic of one walk launch: dram__bytes_read + dram__bytes_write of an ncu capture at the benchmark size
-    # (5.99 GB at B=4, profiles/laplace_forward_b4_h12_n16384_ncu.md); other batches scale it, every array grows with P
-    traffic = 5.99e9 * B / 4
+    # (6.07 GB at B=4, profiles/laplace_forward_b4_h12_n16384_ncu.md); other batches scale it, every array grows with P
+    traffic = 6.07e9 * B / 4
     line = {
         "metric": "q.k pairs/s", "value": pairs / (ms * 1e-3), "unit": "pairs/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,

@@ -1,7 +1,7 @@
 """Speed and memory sweep of kernel attention against softmax attention, with the reference's protocol
 (Experiments/speed_and_memory/bench.py:22-42,83-121): B=4, H=12, D=C=64, N = 2^7 .. 2^17, CUDA events,
-5 warm-up calls, 10 timed calls, mean and standard deviation, peak memory above the inputs; forward for
-add_laplace, forward and forward+backward for add_riesz and softmax. Rows are appended to a CSV and
+5 warm-up calls, 10 timed calls, mean and standard deviation, peak memory above the inputs; forward and
+forward+backward for add_laplace (the reference times it forward only: it has no backward), add_riesz and softmax. Rows are appended to a CSV and
 sizes already present in it are skipped (bench.py:128-131,141). The pykeops columns of the reference are
 absent: this library has no keops backend.
 
@@ -62,7 +62,7 @@ def main():
             w.writeheader()
         for lg in range(a.min_log2, a.max_log2 + 1):
             N = 1 << lg
-            for method, modes in (("add_laplace", ("fwd",)), ("add_riesz", ("fwd", "fwd+bwd")), ("softmax", ("fwd", "fwd+bwd"))):
+            for method, modes in (("add_laplace", ("fwd", "fwd+bwd")), ("add_riesz", ("fwd", "fwd+bwd")), ("softmax", ("fwd", "fwd+bwd"))):
                 for mode in modes:
                     if (method, mode, N) in done:
                         continue

@@ -162,6 +162,45 @@ __device__ __forceinline__ void block_affine_scan(const int cnt, const float (&A
     }
 }
 
+// The same scan with the B terms read from and the results written to shared memory (position i0 + k of `src` / `dst`,
+// which may be the same array): nothing but the coefficients stays in registers between the two sweeps over the run.
+template <int THREADS, int E, bool REV, int OFF>
+__device__ __forceinline__ void block_affine_scan_mem(const int cnt, const int i0, const float (&AA)[E + 1],
+                                                      const float* __restrict__ src, float* __restrict__ dst,
+                                                      float* __restrict__ wa, float* __restrict__ wb)
+{
+    constexpr int W = THREADS / 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float a = 1.0f, b = 0.0f;
+    #pragma unroll
+    for (int kk = 0; kk < E; kk++) {
+        const int k = REV ? E - 1 - kk : kk;
+        if (k < cnt) { a = AA[k + OFF] * a; b = fmaf(AA[k + OFF], b, src[i0 + k]); }
+    }
+    float ia = a, ib = b;
+    #pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        float pa = REV ? __shfl_down_sync(FULL, ia, off) : __shfl_up_sync(FULL, ia, off);
+        float pb = REV ? __shfl_down_sync(FULL, ib, off) : __shfl_up_sync(FULL, ib, off);
+        if (REV ? (lane + off < 32) : (lane >= off)) { ib = fmaf(ia, pb, ib); ia = ia * pa; }
+    }
+    __syncthreads();
+    if (lane == (REV ? 0 : 31)) { wa[warp] = ia; wb[warp] = ib; }
+    __syncthreads();
+    float pb = 0.0f;
+    if (REV) { for (int w = W - 1; w > warp; w--) pb = fmaf(wa[w], pb, wb[w]); }
+    else     { for (int w = 0; w < warp; w++)     pb = fmaf(wa[w], pb, wb[w]); }
+    float ea = REV ? __shfl_down_sync(FULL, ia, 1) : __shfl_up_sync(FULL, ia, 1);
+    float eb = REV ? __shfl_down_sync(FULL, ib, 1) : __shfl_up_sync(FULL, ib, 1);
+    if (lane == (REV ? 31 : 0)) { ea = 1.0f; eb = 0.0f; }
+    float x = fmaf(ea, pb, eb);
+    #pragma unroll
+    for (int kk = 0; kk < E; kk++) {
+        const int k = REV ? E - 1 - kk : kk;
+        if (k < cnt) { x = fmaf(AA[k + OFF], x, src[i0 + k]); dst[i0 + k] = x; }
+    }
+}
+
 // in-place exclusive prefix sum of h[0..n) (n <= THREADS * (E + 1)); returns nothing, h[i] <- sum_{j<i} h[j]
 template <int THREADS, int E>
 __device__ __forceinline__ void block_exclusive_sum(uint32_t* __restrict__ h, const int n, uint32_t* __restrict__ wsum)
@@ -272,22 +311,30 @@ __global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
             for (int k = 0; k < R; k++) bx[k] = dk[k];
             flush(bx, xval);
             for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
-            if (a.scal == SCAL_UNIT || (SIGNED && a.scal == SCAL_SIGNED)) {
-                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)) u_i,  su1[j] = sum_{i>=j} exp(-(k_i - k_j)) u_i, with u == 1 or the
-                // per-key scalar, which waits in the staging buffer (own run only) because su0s overwrites the index payload
-                const float* us = (SIGNED && a.scal == SCAL_SIGNED && a.us) ? a.us + (long long)p * N : nullptr;
-                if (us) {
+            if (SIGNED && a.scal == SCAL_SIGNED) {
+                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)) u_i,  su1[j] = sum_{i>=j} exp(-(k_i - k_j)) u_i with u the per-key scalar
+                // (all ones without one). The scalars wait in the staging buffer, every thread touching only its own run,
+                // because su0s overwrites the index payload; the backward scan runs in place there and leaves through it.
+                {
+                    const float* us = a.us ? a.us + (long long)p * N : nullptr;
+                    __syncthreads();                  // the staging buffer may still be drained by the flush above
                     #pragma unroll
-                    for (int k = 0; k < R; k++) if (k < cntk) stage[i0 + k] = us[sidx[i0 + k]];
+                    for (int k = 0; k < R; k++) if (k < cntk) stage[i0 + k] = us ? us[sidx[i0 + k]] : 1.0f;
                 }
+                block_affine_scan_mem<THREADS, R, false, 0>(cntk, i0, dk, stage, su0s, wa, wb);
+                block_affine_scan_mem<THREADS, R, true, 1>(cntk, i0, dk, stage, stage, wa, wb);
+                __syncthreads();
+                for (int j = tid; j < N; j += THREADS) su1[j] = stage[j];
+            } else if (a.scal == SCAL_UNIT) {
+                // su0[j] = sum_{i<=j} exp(-(k_j - k_i)),  su1[j] = sum_{i>=j} exp(-(k_i - k_j))
                 #pragma unroll
-                for (int k = 0; k < R; k++) bx[k] = us ? (k < cntk ? stage[i0 + k] : 0.0f) : 1.0f;
+                for (int k = 0; k < R; k++) bx[k] = 1.0f;
                 block_affine_scan<THREADS, R, false, 0>(cntk, dk, bx, wa, wb);
                 #pragma unroll
                 for (int k = 0; k < R; k++) if (k < cntk) su0s[i0 + k] = bx[k];     // stays in shared memory
-                // backward over the same runs: R_j = a_{j+1} R_{j+1} + u_j
+                // backward over the same runs: R_j = a_{j+1} R_{j+1} + 1
                 #pragma unroll
-                for (int k = 0; k < R; k++) bx[k] = us ? (k < cntk ? stage[i0 + k] : 0.0f) : 1.0f;
+                for (int k = 0; k < R; k++) bx[k] = 1.0f;
                 block_affine_scan<THREADS, R, true, 1>(cntk, dk, bx, wa, wb);
                 flush(bx, su1);
             }

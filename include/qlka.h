@@ -114,6 +114,16 @@ int qlka_laplace_attention_forward(const float* q, const float* k, const float* 
                                    float tau, float* out, void* workspace, size_t workspace_bytes,
                                    int B, int H, int S, int D, int Dv, qlka_stream_t stream);
 
+/* The same for the two kernels that go through the abs sum (forward only), kind 0 = add_riesz, kind 1 = add_bump:
+ *   add_riesz  A_ij = |q_i|_1 + |k_j|_1 - |q_i - k_j|_1 + 1e-3   (Experiments/kernel_attention/attention.py:75-81)
+ *   add_bump   A_ij = sum_d max(0, 1 - |q_id - k_jd|)             (:84-92; one sort for the three shifted abs sums,
+ *              which limits it to 3 S <= 16384 - longer sequences get QLKA_ERR_UNSUPPORTED and go op by op)
+ * with q and k divided by tau first; out = A v / max(row sum of A, 1e-6) over the kept keys. */
+int qlka_abs_attention_workspace_bytes(int kind, int B, int H, int S, int D, int Dv, int masked, size_t* bytes);
+int qlka_abs_attention_forward(int kind, const float* q, const float* k, const float* v, const float* keep /* nullable */,
+                               float tau, float* out, void* workspace, size_t workspace_bytes,
+                               int B, int H, int S, int D, int Dv, qlka_stream_t stream);
+
 /* ---- weighted abs sum, forward ---------------------------------------------------------
  * out_w[p,m,c] = sum_{d,n} |k[p,d,n] - q[p,d,m]| v[p,n,c]           (P, M, C)
  * out_u[p,m]   = sum_{d,n} |k[p,d,n] - q[p,d,m]|                    (P, M), optional (NULL)

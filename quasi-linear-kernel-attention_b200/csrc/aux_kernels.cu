@@ -7,14 +7,15 @@
 
 namespace qlka {
 
-// out[p, l] = sum_d x[p, d, l]
+// out[p, l] = sum_d x[p, d, l]   (ABS: sum_d |x[p, d, l]|)
+template <bool ABS>
 __global__ void colsum_d_kernel(const float* __restrict__ x, float* __restrict__ out, const int D, const int L, const long long total) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long p = i / L, l = i % L;
     const float* src = x + p * D * L + l;
     float acc = 0.0f;
-    for (int d = 0; d < D; d++) acc += src[(long long)d * L];
+    for (int d = 0; d < D; d++) { const float t = src[(long long)d * L]; acc += ABS ? fabsf(t) : t; }
     out[i] = acc;
 }
 
@@ -160,12 +161,14 @@ __global__ void __launch_bounds__(256) npad_kernel(const float* __restrict__ kee
     if (threadIdx.x == 0) n_pad[b] = (float)S - red[0];
 }
 
-// out[p, m, :] /= max(out_u[p, m] - n_pad[p / H] * sum_d exp(-|qt[p, d, m]|), clamp): the row normalisation of
-// _add_laplace, with the row sum corrected for the masked keys (each sits at k = 0 with v = 0). One warp per row.
-__global__ void __launch_bounds__(256) laplace_normalise_kernel(float* __restrict__ out, const float* __restrict__ out_u,
-                                                                const float* __restrict__ qt, const float* __restrict__ n_pad,
-                                                                const int M, const int D, const int C, const int H,
-                                                                const float clamp, const long long rows)
+// out[p, m, :] /= max(out_u[p, m] - n_pad[p / H] * sum_d f(qt[p, d, m]), clamp): the row normalisation of _add_laplace
+// (BUMP = false, f(x) = exp(-|x|)) and of _add_bump (BUMP = true, f(x) = max(0, 1 - |x|)), with the row sum corrected for
+// the masked keys (each sits at k = 0 with v = 0 and adds f(q_d) per dimension). One warp per row.
+template <bool BUMP>
+__global__ void __launch_bounds__(256) normalise_kernel(float* __restrict__ out, const float* __restrict__ out_u,
+                                                        const float* __restrict__ qt, const float* __restrict__ n_pad,
+                                                        const int M, const int D, const int C, const int H,
+                                                        const float clamp, const long long rows)
 {
     const long long row  = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     const int       lane = threadIdx.x & 31;
@@ -176,7 +179,10 @@ __global__ void __launch_bounds__(256) laplace_normalise_kernel(float* __restric
         const float np = n_pad[p / H];
         if (np != 0.0f) {
             float acc = 0.0f;
-            for (int d = lane; d < D; d += 32) acc += __expf(-fabsf(qt[(p * D + d) * M + m]));
+            for (int d = lane; d < D; d += 32) {
+                const float x = fabsf(qt[(p * D + d) * M + m]);
+                acc += BUMP ? fmaxf(0.0f, 1.0f - x) : __expf(-x);
+            }
             #pragma unroll
             for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(FULL, acc, off);
             den -= np * acc;
@@ -187,11 +193,38 @@ __global__ void __launch_bounds__(256) laplace_normalise_kernel(float* __restric
     for (int c = lane; c < C; c += 32) o[c] *= inv;
 }
 
+// The add_riesz epilogue (Experiments/kernel_attention/attention.py:75-81), in place on out = the weighted abs sum:
+//   a = aq[p, m] + eps;  num = a * vsum[p, :] + akv[p, :] - out;  den = a * S + aksum[p] - out_u[p, m] - eps * n_pad[p / H]
+//   out = num / max(den, clamp).   One warp per row.
+__global__ void __launch_bounds__(256) riesz_epilogue_kernel(float* __restrict__ out, const float* __restrict__ out_u,
+                                                             const float* __restrict__ aq, const float* __restrict__ vsum,
+                                                             const float* __restrict__ akv, const float* __restrict__ aksum,
+                                                             const float* __restrict__ n_pad,
+                                                             const int M, const int C, const int C4, const int H,
+                                                             const float eps, const float clamp, const long long rows)
+{
+    const long long row  = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    const int       lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const long long p = row / M;
+    const float a   = aq[row] + eps;
+    const float np  = n_pad ? n_pad[p / H] : 0.0f;
+    const float den = a * (float)M + aksum[p] - out_u[row] - eps * np;
+    const float inv = 1.0f / fmaxf(den, clamp);
+    float* o = out + row * C;
+    for (int c = lane; c < C; c += 32) o[c] = (fmaf(a, vsum[p * C4 + c], akv[p * C4 + c]) - o[c]) * inv;
+}
+
 static inline unsigned blocks_for(long long total, int threads) { return (unsigned)((total + threads - 1) / threads); }
 
 cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st) {
     const long long total = (long long)P * L;
-    colsum_d_kernel<<<blocks_for(total, 256), 256, 0, st>>>(x, out, D, L, total);
+    colsum_d_kernel<false><<<blocks_for(total, 256), 256, 0, st>>>(x, out, D, L, total);
+    return cudaGetLastError();
+}
+cudaError_t launch_abscolsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st) {
+    const long long total = (long long)P * L;
+    colsum_d_kernel<true><<<blocks_for(total, 256), 256, 0, st>>>(x, out, D, L, total);
     return cudaGetLastError();
 }
 cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st) {
@@ -234,10 +267,18 @@ cudaError_t launch_npad(const float* keep, float* n_pad, int B, int S, cudaStrea
     npad_kernel<<<B, 256, 0, st>>>(keep, n_pad, S);
     return cudaGetLastError();
 }
-cudaError_t launch_laplace_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
-                                     int P, int M, int D, int C, int H, float clamp, cudaStream_t st) {
+cudaError_t launch_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
+                             int P, int M, int D, int C, int H, float clamp, bool bump, cudaStream_t st) {
     const long long rows = (long long)P * M;
-    laplace_normalise_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(out, out_u, qt, n_pad, M, D, C, H, clamp, rows);
+    if (bump) normalise_kernel<true><<<blocks_for(rows, 8), 256, 0, st>>>(out, out_u, qt, n_pad, M, D, C, H, clamp, rows);
+    else      normalise_kernel<false><<<blocks_for(rows, 8), 256, 0, st>>>(out, out_u, qt, n_pad, M, D, C, H, clamp, rows);
+    return cudaGetLastError();
+}
+cudaError_t launch_riesz_epilogue(float* out, const float* out_u, const float* aq, const float* vsum, const float* akv,
+                                  const float* aksum, const float* n_pad, int P, int M, int C, int C4, int H,
+                                  float eps, float clamp, cudaStream_t st) {
+    const long long rows = (long long)P * M;
+    riesz_epilogue_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(out, out_u, aq, vsum, akv, aksum, n_pad, M, C, C4, H, eps, clamp, rows);
     return cudaGetLastError();
 }
 

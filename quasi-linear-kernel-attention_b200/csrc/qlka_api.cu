@@ -25,8 +25,12 @@ cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int 
 cudaError_t launch_transpose_scale(const float* src, float* dst, const float* keep, float scale, int P, int S, int D, int H, cudaStream_t st);
 cudaError_t launch_mask_rows(const float* src, float* dst, const float* keep, int P, int S, int C, int H, cudaStream_t st);
 cudaError_t launch_npad(const float* keep, float* n_pad, int B, int S, cudaStream_t st);
-cudaError_t launch_laplace_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
-                                     int P, int M, int D, int C, int H, float clamp, cudaStream_t st);
+cudaError_t launch_normalise(float* out, const float* out_u, const float* qt, const float* n_pad,
+                             int P, int M, int D, int C, int H, float clamp, bool bump, cudaStream_t st);
+cudaError_t launch_abscolsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st);
+cudaError_t launch_riesz_epilogue(float* out, const float* out_u, const float* aq, const float* vsum, const float* akv,
+                                  const float* aksum, const float* n_pad, int P, int M, int C, int C4, int H,
+                                  float eps, float clamp, cudaStream_t st);
 }  // namespace qlka
 
 using namespace qlka;
@@ -438,7 +442,93 @@ int qlka_laplace_attention_forward(const float* q, const float* k, const float* 
     }
     st = laplace_forward_impl(ws.qt, ws.kt, rows, out, ws.out_u, ws.inner, ws.inner_bytes, P, D, S, S, Dv, stream, nullptr);
     if (st) return st;
-    CU(launch_laplace_normalise(out, ws.out_u, ws.qt, ws.n_pad, P, S, D, Dv, H, 1e-6f, stream));
+    CU(launch_normalise(out, ws.out_u, ws.qt, ws.n_pad, P, S, D, Dv, H, 1e-6f, false, stream));
+    return QLKA_OK;
+}
+
+// ---------------------------------------------------------------- add_riesz / add_bump attention on (B, H, S, D)
+static int abs_forward_impl(const float* q, const float* k, const float* v, float* out_w, float* out_u,
+                            void* workspace, size_t workspace_bytes, int P, int D, int N, int M, int C,
+                            int ns, const float* shifts, const float* weights, cudaStream_t stream);
+namespace {
+constexpr float BUMP_SHIFTS[3]  = {0.0f, 1.0f, -1.0f};     // max(0, 1 - |x|) = |x + 1| / 2 + |x - 1| / 2 - |x|
+constexpr float BUMP_WEIGHTS[3] = {-1.0f, 0.5f, 0.5f};
+struct AbsAttnWs {
+    float *qt, *kt, *vm, *out_u, *n_pad, *aq, *ak, *sums /* vsum | akv | aksum */; void* inner; size_t inner_bytes, bytes;
+    AbsAttnWs(void* base, int B, int H, int S, int D, int C, bool masked, bool bump) {
+        Bump b(base);
+        const size_t P = (size_t)B * H;
+        qt    = b.take<float>(P * D * S);
+        kt    = b.take<float>(P * D * S);
+        vm    = masked ? b.take<float>(P * S * C) : nullptr;
+        out_u = b.take<float>(P * S);
+        n_pad = masked ? b.take<float>((size_t)B) : nullptr;
+        aq    = bump ? nullptr : b.take<float>(P * S);
+        ak    = bump ? nullptr : b.take<float>(P * S);
+        sums  = bump ? nullptr : b.take<float>(P * C * 2 + P);
+        inner_bytes = AbsFwdWs(nullptr, (int)P, D, S, bump ? 3 * S : S, C).bytes;
+        inner = b.take<unsigned char>(inner_bytes);
+        bytes = (b.off + 255) & ~size_t(255);
+    }
+};
+}  // namespace
+
+static int abs_attn_check(int kind, int B, int H, int S, int D, int C) {
+    if (kind != 0 && kind != 1) return QLKA_ERR_PATH;
+    int st = attn_check(B, H, S, D, C);
+    if (st) return st;
+    if (kind == 1 && 3LL * S > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;     // the three shifted query copies share one shared-memory sort
+    return QLKA_OK;
+}
+
+int qlka_abs_attention_workspace_bytes(int kind, int B, int H, int S, int D, int Dv, int masked, size_t* bytes) {
+    if (!bytes) return QLKA_ERR_NULL;
+    int st = abs_attn_check(kind, B, H, S, D, Dv);
+    if (st) return st;
+    *bytes = AbsAttnWs(nullptr, B, H, S, D, Dv, masked != 0, kind == 1).bytes;
+    return QLKA_OK;
+}
+
+int qlka_abs_attention_forward(int kind, const float* q, const float* k, const float* v, const float* keep, float tau,
+                               float* out, void* workspace, size_t workspace_bytes,
+                               int B, int H, int S, int D, int Dv, qlka_stream_t stream_)
+{
+    int st = abs_attn_check(kind, B, H, S, D, Dv);
+    if (st) return st;
+    if (!q || !k || !v || !out) return QLKA_ERR_NULL;
+    if (!(tau > 0.0f)) return QLKA_ERR_BAD_SHAPE;
+    const bool masked = keep != nullptr, bump = kind == 1;
+    AbsAttnWs ws(workspace, B, H, S, D, Dv, masked, bump);
+    if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const int P = B * H;
+
+    CU(launch_transpose_scale(q, ws.qt, nullptr, 1.0f / tau, P, S, D, H, stream));
+    CU(launch_transpose_scale(k, ws.kt, keep, 1.0f / tau, P, S, D, H, stream));
+    const float* rows = v;
+    if (masked) {
+        CU(launch_mask_rows(v, ws.vm, keep, P, S, Dv, H, stream));
+        CU(launch_npad(keep, ws.n_pad, B, S, stream));
+        rows = ws.vm;
+    }
+    if (bump) {
+        // numerator and row sum of the three shifted abs sums from one sort, then the row normalisation
+        st = abs_forward_impl(ws.qt, ws.kt, rows, out, ws.out_u, ws.inner, ws.inner_bytes, P, D, S, S, Dv, 3, BUMP_SHIFTS, BUMP_WEIGHTS, stream);
+        if (st) return st;
+        CU(launch_normalise(out, ws.out_u, ws.qt, ws.n_pad, P, S, D, Dv, H, 1e-6f, true, stream));
+    } else {
+        // A_ij = |q_i|_1 + |k_j|_1 - |q_i - k_j|_1 + eps: rank-1 terms from column and row statistics, the abs sum from the walk
+        float* vsum  = ws.sums;
+        float* akv   = vsum + (size_t)P * Dv;
+        float* aksum = akv + (size_t)P * Dv;
+        CU(launch_abscolsum_d(ws.qt, ws.aq, P, D, S, stream));
+        CU(launch_abscolsum_d(ws.kt, ws.ak, P, D, S, stream));
+        CU(cudaMemsetAsync(ws.sums, 0, sizeof(float) * ((size_t)P * Dv * 2 + P), stream));
+        CU(launch_rowstat(rows, ws.ak, vsum, akv, aksum, P, S, Dv, stream));
+        st = abs_forward_impl(ws.qt, ws.kt, rows, out, ws.out_u, ws.inner, ws.inner_bytes, P, D, S, S, Dv, 0, nullptr, nullptr, stream);
+        if (st) return st;
+        CU(launch_riesz_epilogue(out, ws.out_u, ws.aq, vsum, akv, aksum, ws.n_pad, P, S, Dv, Dv, H, 1e-3f, 1e-6f, stream));
+    }
     return QLKA_OK;
 }
 

@@ -68,9 +68,9 @@ def attention(q, k, v, kernel, tau, keep=None):
     B, H, S, D = q.shape
     P = B * H
     needs_grad = torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad)
-    if kernel == "add_laplace" and not needs_grad:
-        # inference: layout change, tau, masking, the sum and the normalisation in one native call
-        return _native.laplace_attention(q, k, v, tau, keep)
+    if not needs_grad and (kernel != "add_bump" or 3 * S <= 16384):
+        # inference: layout change, tau, masking, the sums and the normalisation in one native call
+        return _native.fused_attention(kernel, q, k, v, tau, keep)
     q = q.transpose(2, 3).reshape(P, D, S)
     k = k.transpose(2, 3).reshape(P, D, S)
     v = v.reshape(P, S, v.shape[3])

@@ -44,6 +44,10 @@ def lib():
         L.qlka_laplace_attention_workspace_bytes.argtypes = [_i] * 6 + [ctypes.POINTER(_sz)]
         L.qlka_laplace_attention_forward.restype = _i
         L.qlka_laplace_attention_forward.argtypes = [_vp] * 4 + [ctypes.c_float] + [_vp] + [_vp, _sz] + [_i] * 5 + [_vp]
+        L.qlka_abs_attention_workspace_bytes.restype = _i
+        L.qlka_abs_attention_workspace_bytes.argtypes = [_i] * 7 + [ctypes.POINTER(_sz)]
+        L.qlka_abs_attention_forward.restype = _i
+        L.qlka_abs_attention_forward.argtypes = [_i] + [_vp] * 4 + [ctypes.c_float] + [_vp] + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_laplace_forward_stage_ms.restype = _i
         L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 2
         L.qlka_noalloc_scratch_bytes.restype = _sz
@@ -290,8 +294,12 @@ def abs_backward(q, k, v, g_w, g_u=None):
     return gq, gk, gv
 
 
-def laplace_attention(q, k, v, tau, keep=None):
-    """Normalised add_laplace attention on (B, H, S, D) / (B, H, S, Dv) tensors in one native call (forward only)."""
+ATTENTION_KINDS = {"add_laplace": -1, "add_riesz": 0, "add_bump": 1}
+
+
+def fused_attention(kernel, q, k, v, tau, keep=None):
+    """Normalised additive-kernel attention on (B, H, S, D) / (B, H, S, Dv) tensors in one native call (forward only)."""
+    kind = ATTENTION_KINDS[kernel]
     _check(q.is_cuda and k.is_cuda and v.is_cuda, "q, k, and v must be CUDA tensors")
     _check(q.dtype == k.dtype == v.dtype == torch.float32, "q, k, and v must be float32")
     _check(q.dim() == 4 and k.shape == q.shape and v.dim() == 4 and v.shape[:3] == q.shape[:3],
@@ -305,17 +313,28 @@ def laplace_attention(q, k, v, tau, keep=None):
     L = lib()
     with torch.cuda.device(q.device):
         n = _sz(0)
-        st = L.qlka_laplace_attention_workspace_bytes(B, H, S, D, Dv, int(keep is not None), ctypes.byref(n))
+        if kind < 0:
+            st = L.qlka_laplace_attention_workspace_bytes(B, H, S, D, Dv, int(keep is not None), ctypes.byref(n))
+        else:
+            st = L.qlka_abs_attention_workspace_bytes(kind, B, H, S, D, Dv, int(keep is not None), ctypes.byref(n))
         if st:
             _raise(st)
         ws = torch.empty(max(int(n.value), 1), dtype=torch.uint8, device=q.device)
         out = torch.empty(B, H, S, Dv, dtype=torch.float32, device=q.device)
-        st = L.qlka_laplace_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                                              None if keep is None else keep.data_ptr(), float(tau), out.data_ptr(),
+        kp = None if keep is None else keep.data_ptr()
+        if kind < 0:
+            st = L.qlka_laplace_attention_forward(q.data_ptr(), k.data_ptr(), v.data_ptr(), kp, float(tau), out.data_ptr(),
+                                                  ws.data_ptr(), int(n.value), B, H, S, D, Dv, _stream())
+        else:
+            st = L.qlka_abs_attention_forward(kind, q.data_ptr(), k.data_ptr(), v.data_ptr(), kp, float(tau), out.data_ptr(),
                                               ws.data_ptr(), int(n.value), B, H, S, D, Dv, _stream())
     if st:
         _raise(st)
     return out
+
+
+def laplace_attention(q, k, v, tau, keep=None):
+    return fused_attention("add_laplace", q, k, v, tau, keep)
 
 
 def laplace_backward(q, k, v, g_w, g_u=None):

@@ -166,3 +166,38 @@ def test_shifted_sum_equals_separate_sums(shape):
     w2, u2 = weighted_abs_sum_shifted(q, k, v, (0.25,), (2.0,))
     a, b = sorted_scan.abs_sum(q + 0.25, k, v)
     assert rel_err(w2, 2 * a) < TOL and rel_err(u2, 2 * b) < TOL
+
+
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("kernel", ["add_riesz", "add_bump"])
+@pytest.mark.parametrize("shape", [(1, 2, 50, 8, 8), (2, 3, 333, 16, 20), (1, 4, 1024, 32, 32), (2, 2, 700, 64, 33)])
+def test_fused_attention_entry(shape, kernel, masked):
+    """add_riesz / add_bump attention in one native call on (B, H, S, D) against the float64 dense formula and the op-by-op route."""
+    import qlka_native
+    from kernel_attention import TAU, attention
+    from oracle import direct
+    B, H, S, D, Dv = shape
+    g = torch.Generator().manual_seed(S + D)
+    q, k = (torch.randn(B, H, S, D, generator=g).cuda() for _ in range(2))
+    v = torch.randn(B, H, S, Dv, generator=g).cuda()
+    keep = None
+    if masked:
+        keep = (torch.rand(B, S, generator=g) > 0.3)
+        keep[:, 0] = True
+        keep = keep.cuda()
+    tau = TAU[kernel]
+    out = qlka_native.fused_attention(kernel, q, k, v, tau, keep)
+    ref = direct.attention(q, k, v, kernel, tau, keep)
+    assert out.shape == (B, H, S, Dv)
+    assert rel_err(out, ref) < 2e-4, f"rel err {rel_err(out, ref)}"
+    with torch.enable_grad():
+        qg = q.clone().requires_grad_(True)
+        slow = attention(qg, k, v, kernel, tau, keep)                      # op-by-op route
+    assert rel_err(out, slow.double()) < 2e-4
+
+
+def test_fused_bump_refuses_long_sequences():
+    import qlka_native
+    q = torch.zeros(1, 1, 6000, 4, device="cuda")
+    with pytest.raises(RuntimeError):
+        qlka_native.fused_attention("add_bump", q, q, q, 1.5)

@@ -1,5 +1,5 @@
 """TEST INFRASTRUCTURE ONLY - compiles the reference's two CUDA extensions for sm_100 from the
-sources where they lie (default /root/reference), into oracle/_ref/ (git-ignored; binaries only,
+sources where they lie (the checkout given on the command line, or the default of `build`), into oracle/_ref/ (git-ignored; binaries only,
 no reference source is copied). The reference's setup.py is not used: this is a direct
 torch.utils.cpp_extension build of its csrc files with its own flags (-O3 --use_fast_math,
 Weighted_*_Sum/setup.py:20-26) and an sm_100 target, which the reference's default arch list

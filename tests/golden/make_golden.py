@@ -1,6 +1,6 @@
 """Generates the golden vectors in this folder from the reference's own Python code.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has the reference checkout (its path is the argument; the default is in the code below):
 
     python tests/golden/make_golden.py [/path/to/reference]
 

@@ -246,7 +246,7 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 // which the walk does not care about.
 // SIGNED builds the SCAL_SIGNED side channel in (a separate instance keeps its registers out of the others).
 template <int THREADS, int E, bool SIGNED>
-__global__ void __launch_bounds__(THREADS, 1) sort_rank_small(const SortArgs a)
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const SortArgs a)
 {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;

@@ -457,8 +457,8 @@ cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream) {
     const int mx = a.N > a.M ? a.N : a.M;
     if (mx <= 1024)  return launch_one<256, 4>(a, stream);
     if (mx <= 2048)  return launch_one<256, 8>(a, stream);
-    if (mx <= 4096)  return launch_one<512, 8>(a, stream);
-    if (mx <= 8192)  return launch_one<1024, 8>(a, stream);
+    if (mx <= 4096)  return launch_one<256, 16>(a, stream);
+    if (mx <= 8192)  return launch_one<512, 16>(a, stream);
     if (mx <= 16384) return launch_one<1024, 16>(a, stream);
     return cudaErrorInvalidValue;
 }

@@ -36,6 +36,12 @@ def build(ref="/root/reference"):
         print("built", os.path.join(bdir, name + ".so"))
 
 
+def load_ref_paths():
+    """Paths of the built extensions that exist."""
+    paths = [os.path.join(OUT, name, name + ".so") for name in EXTS]
+    return [p for p in paths if os.path.exists(p)]
+
+
 def load_ref():
     """{'laplace': module, 'abs': module} for the extensions found under oracle/_ref, else {}."""
     import torch  # noqa: F401  (the extensions link against libtorch)

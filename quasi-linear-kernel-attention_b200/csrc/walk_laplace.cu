@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                     }
                 }
                 // the block's queries, in rank order
-                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record (row 0 for the sentinel)
+                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record
                     const float* gr = g + (size_t)rec.z * C4;
                     #pragma unroll
                     for (int c = 0; c < CPL; c += 4) {
@@ -275,7 +275,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                     __syncwarp(gmask);                // every lane has its rows in registers: the slot may hold partial dots
                 }
                 if (cnt < (uint32_t)LPS) {
-                    // usual case: every record of the block and a closing sentinel sit in the staged slot
+                    // usual case: every record of the block sits in the staged slot, followed by a record of a later rank
                     uint32_t qa  = f.qs_s + cur * LPS * 16;
                     uint4    rec = lds128u(qa);
                     uint32_t n = 0, nb = min(cnt, (uint32_t)G_SLOTS);      // records [0, nb) have their emit-side rows staged

@@ -183,7 +183,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS :
                         }
                     }
                 }
-                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record (row 0 for the sentinel)
+                auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record
                     const float* gr = g + (size_t)rec.z * C4;
                     #pragma unroll
                     for (int c = 0; c < CPL; c += 4) {

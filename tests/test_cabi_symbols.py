@@ -78,3 +78,27 @@ def test_ops_fail_loudly_without_cuda_tensors(lib):
         weighted_abs_sum(q, k, v)
     with pytest.raises(ValueError):
         weighted_abs_sum(q, k, v, backend="nope")
+
+
+def test_newer_entry_points_check_their_arguments(lib):
+    n, m = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    # Laplace backward: same dimension rules, a workspace at least as large as the forward's records
+    assert lib.qlka_laplace_backward_workspace_bytes(2, 4, 512, 300, 64, ctypes.byref(n)) == 0
+    assert lib.qlka_laplace_forward_workspace_bytes(2, 4, 512, 300, 64, ctypes.byref(m)) == 0
+    assert n.value >= m.value > 0
+    assert lib.qlka_laplace_backward_workspace_bytes(2, 4, 512, 300, 0, ctypes.byref(n)) == 2
+    assert lib.qlka_weighted_laplace_sum_backward(None, None, None, None, None, None, None, None, None, 0, 1, 1, 8, 8, 4, None) == 7
+    # attention entry points: kind, head count, sequence limit of the fused bump, tau
+    assert lib.qlka_laplace_attention_workspace_bytes(2, 3, 100, 16, 16, 0, ctypes.byref(n)) == 0 and n.value > 0
+    assert lib.qlka_laplace_attention_workspace_bytes(2, 3, 100, 16, 16, 1, ctypes.byref(m)) == 0 and m.value > n.value
+    assert lib.qlka_laplace_attention_workspace_bytes(0, 3, 100, 16, 16, 0, ctypes.byref(n)) == 1
+    assert lib.qlka_abs_attention_workspace_bytes(2, 1, 1, 100, 16, 16, 0, ctypes.byref(n)) == 5          # kind is 0 or 1
+    assert lib.qlka_abs_attention_workspace_bytes(1, 1, 1, 6000, 16, 16, 0, ctypes.byref(n)) == 10        # fused bump: 3 S <= 16384
+    assert lib.qlka_abs_attention_workspace_bytes(0, 1, 1, 6000, 16, 16, 0, ctypes.byref(n)) == 0
+    f = lib.qlka_abs_attention_forward
+    assert f(0, None, None, None, None, ctypes.c_float(1.0), None, None, 0, 1, 1, 8, 4, 4, None) == 7     # null tensors
+    assert f(0, 1, 1, 1, None, ctypes.c_float(0.0), 1, None, 0, 1, 1, 8, 4, 4, None) == 1                 # tau must be > 0
+    # shifted abs sum and the fixed-scratch Laplace entry refuse what they cannot hold
+    assert lib.qlka_abs_shifted_forward_workspace_bytes(1, 1, 100, 6000, 8, 3, ctypes.byref(n)) == 10
+    assert lib.qlka_abs_shifted_forward_workspace_bytes(1, 1, 100, 100, 8, 5, ctypes.byref(n)) == 1
+    assert lib.qlka_noalloc_scratch_bytes() == 32 << 20

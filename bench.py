@@ -120,6 +120,53 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+# ------------------------------------------------------------------ the training-step workload (not the headline)
+def run_abs_fwd_bwd(args):
+    """weighted_abs_sum_full forward + backward at B=8, H=12, N=4096, D=Dv=64 (the add_riesz training step of the
+    reference's configurations): one GPU, device-resident inputs, one JSON line of the same shape without the host legs."""
+    from weighted_abs_sum import weighted_abs_sum_full
+    Pc, Dc, Nc, Cc = 8 * 12, 64, 4096, 64
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(0)
+    q = (torch.randn(Pc, Dc, Nc, generator=g) * 0.5).to(dev).requires_grad_(True)
+    k = (torch.randn(Pc, Dc, Nc, generator=g) * 0.5).to(dev).requires_grad_(True)
+    v = torch.randn(Pc, Nc, Cc, generator=g).to(dev).requires_grad_(True)
+    g_w = torch.randn(Pc, Nc, Cc, generator=g).to(dev)
+    g_u = torch.randn(Pc, Nc, generator=g).to(dev)
+
+    def step():
+        q.grad = k.grad = v.grad = None
+        out_w, out_u = weighted_abs_sum_full(q, k, v)
+        torch.autograd.backward((out_w, out_u), (g_w, g_u))
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(args.steps):
+            step()                                      # inputs and gradients (7 x 96 MiB + 2 x 1.5 MiB) exceed the 126 MB L2
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+    peak, which = measured_peaks()
+    pairs = Pc * Dc * Nc * Nc
+    # every tensor once: forward reads q, k, v and writes out_w, out_u; backward reads q, k, v, g_w, g_u and writes three gradients
+    algo = 4 * Pc * ((Dc * Nc * 2 + Nc * Cc * 2 + Nc) + (Dc * Nc * 4 + Nc * Cc * 3 + Nc))
+    achieved = algo / (ms * 1e-3) / 1e9
+    line = {"metric": "q.k pairs/s", "value": pairs / (ms * 1e-3), "unit": "pairs/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "weighted_abs_sum_full forward+backward B=8 H=12 N=M=4096 D=64 Dv=64 fp32 (q,k~0.5*N(0,1), v,g~N(0,1), seed 0)",
+                       "l2": "inputs larger than L2"},
+            "clocks": clocks.summary(), "gpu_launches": 16 * args.steps,      # 6 kernels of the forward, 10 of the backward
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": which, "algorithmic_bytes": algo, "kernel": "whole forward+backward step"}}
+    print(json.dumps(line), flush=True)
+
+
 # ------------------------------------------------------------------ ours
 def run_ours(args, rank, world, local_rank):
     import qlka_native
@@ -226,6 +273,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=B, help="B of the workload (default: the benchmark's 4; smaller for profiler captures)")
+    ap.add_argument("--workload", default="laplace_fwd", choices=["laplace_fwd", "abs_fwd_bwd"],
+                    help="laplace_fwd: the headline benchmark (default); abs_fwd_bwd: the abs-sum training step, one GPU, device timing only")
     args = ap.parse_args()
     if args.batch != B:
         B = args.batch
@@ -238,6 +287,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
         run_reference(args, rank)
+        return
+    if args.workload == "abs_fwd_bwd":
+        if rank == 0:
+            run_abs_fwd_bwd(args)
         return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")

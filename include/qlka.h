@@ -10,6 +10,11 @@
  * Shapes (row-major): q (P, D, M) queries, k (P, D, N) keys, v (P, N, C) values,
  * g_w / g (P, M, C), g_u (P, M), with P = batch * heads.
  *
+ * Alignment: the row matrices - v, g_w, g, out_w, grad_v and the `out` of the attention entry
+ * points - must start on a 16-byte boundary (the kernels move their rows with 16-byte copies and
+ * vector reductions); anything else returns QLKA_ERR_ALIGNMENT before a kernel is launched.
+ * q, k, g_u, out_u, grad_q and grad_k only need float alignment. The workspace needs 256 bytes.
+ *
  * Limits shared by all entry points (those of the reference's check_qkv,
  * Weighted_Abs_Sum/csrc/binding.cpp:69-84 and Weighted_Laplace_Sum/csrc/binding.cpp:66-79):
  * P, D, N, M > 0, 1 <= C <= 128, P * D * max(N, M) <= INT32_MAX; N, M <= 262144 here (the reference
@@ -39,7 +44,8 @@ enum qlka_status {
     QLKA_ERR_WORKSPACE = 8,        /* workspace too small or misaligned (256 bytes) */
     QLKA_ERR_CUDA = 9,             /* a CUDA runtime call failed; see qlka_last_cuda_error */
     QLKA_ERR_UNSUPPORTED = 10,     /* a size inside the limits that this build has no kernel for */
-    QLKA_ERR_NO_ALLOC_LIMIT = 11   /* problem too large for the fixed scratch of the *_noalloc entry point */
+    QLKA_ERR_NO_ALLOC_LIMIT = 11,  /* problem too large for the fixed scratch of the *_noalloc entry point */
+    QLKA_ERR_ALIGNMENT = 12        /* a row matrix (v, g_w, g, out_w, grad_v, attention out) is not 16-byte aligned */
 };
 
 /* Human-readable text of a status code (static storage). */
@@ -65,8 +71,11 @@ int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const floa
  * the library image; every GPU that loads the library keeps that much reserved until the process
  * exits. Problems whose scratch would not fit are refused with QLKA_ERR_NO_ALLOC_LIMIT (roughly:
  * P*D*(N+M) above a few hundred thousand elements) - use the workspace variant for those. The call
- * allocates nothing and frees nothing. The first call on each device looks up the array's device
- * address (one cheap runtime query); make that call once outside any stream capture. All calls
+ * allocates nothing and frees nothing once the array exists: with CUDA's default lazy module loading
+ * the array is materialised by the first call on each device (which looks up its device address), or
+ * at load time under CUDA_MODULE_LOADING=EAGER. So make one call per device at start-up, before the
+ * host's own pool has taken the memory and outside any stream capture; that first call is the one that
+ * can fail with QLKA_ERR_CUDA (out of memory), later ones leave free device memory untouched. All calls
  * share the one array: two calls whose kernels can overlap on the GPU (different streams, or
  * different host threads) corrupt each other, so serialise them. Nothing needs to be cleared
  * between calls. This entry point has no counterpart in the reference, whose operators allocate

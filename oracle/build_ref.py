@@ -1,11 +1,11 @@
 """TEST INFRASTRUCTURE ONLY - compiles the reference's two CUDA extensions for sm_100 from the
-sources where they lie (the checkout given on the command line, or the default of `build`), into oracle/_ref/ (git-ignored; binaries only,
+sources where they lie (the checkout given on the command line or in QLKA_REFERENCE_DIR), into oracle/_ref/ (git-ignored; binaries only,
 no reference source is copied). The reference's setup.py is not used: this is a direct
 torch.utils.cpp_extension build of its csrc files with its own flags (-O3 --use_fast_math,
 Weighted_*_Sum/setup.py:20-26) and an sm_100 target, which the reference's default arch list
 lacks (setup.py:6).
 
-    python oracle/build_ref.py [/path/to/reference]
+    python oracle/build_ref.py /path/to/reference
 
 `load_ref()` imports the built modules (on the GPU box the sources are absent; only the
 prebuilt .so files are used). They serve as a second parity checker for the GPU tests and
@@ -24,7 +24,8 @@ EXTS = {
 }
 
 
-def build(ref="/root/reference"):
+def build(ref):
+    """Compile both extensions from the checkout at `ref`."""
     from torch.utils.cpp_extension import load
     os.environ.setdefault("CXX", "/usr/bin/g++")
     os.environ["TORCH_CUDA_ARCH_LIST"] = "10.0"
@@ -57,4 +58,7 @@ def load_ref():
 
 
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QLKA_REFERENCE_DIR")
+    if not where:
+        sys.exit("usage: python oracle/build_ref.py /path/to/reference   (or set QLKA_REFERENCE_DIR)")
+    build(where)

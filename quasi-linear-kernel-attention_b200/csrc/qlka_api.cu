@@ -5,7 +5,6 @@
 #include "qlka_common.cuh"
 
 #include <climits>
-#include <cstdlib>
 
 namespace qlka {
 cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
@@ -71,15 +70,19 @@ struct Bump {
     }
 };
 
+// SM count of the current device, looked up once per device (racing first calls store the same value; int stores
+// are atomic on every host this library builds for)
 int sm_count() {
-    static int cached = 0;
-    if (!cached) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-            n = 148;                               // B200; also keeps workspace sizes defined without a device
-        cached = n;
+    constexpr int MAX_DEV = 64;
+    static int cached[MAX_DEV] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 148;      // B200; keeps workspace sizes defined without a device
+    if (!cached[dev]) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
     }
-    return cached;
+    return cached[dev];
 }
 
 // how a walk over `nseg` segments of N keys is cut into streams, items and CTAs
@@ -88,8 +91,7 @@ struct WalkPlan { int sps, segs, nitems, grid; };
 WalkPlan plan_walk(int nseg, int N, int C4) {
     const int lps      = walk_lanes_per_stream(C4);
     const int streams  = walk_threads() / lps;
-    int per_sm = C4 <= 64 ? 2 : 1;              // resident walk CTAs per SM (registers and shared memory)
-    if (const char* e = std::getenv("QLKA_WALK_CTAS_PER_SM")) { const int v = std::atoi(e); if (v >= 1 && v <= 8) per_sm = v; }   // tuning aid
+    const int per_sm = C4 <= 64 ? 2 : 1;        // resident walk CTAs per SM (registers and shared memory)
     const int grid_cap = sm_count() * per_sm;
     const int nbk      = nblocks(N);
     // streams per segment: a divisor of the CTA's stream count; more of them until there are enough items to
@@ -149,6 +151,11 @@ WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int n
 // channels as the kernels see them: padded to the lane granularity of the walk (4 floats up to 64
 // channels, 8 floats above, where a lane owns 8 channels)
 inline int round4(int C) { return C <= 64 ? (C + 3) & ~3 : (C + 7) & ~7; }
+
+// The row matrices (v, g_w, g, out_w, grad_v, the attention output) are read and written with 16-byte copies,
+// loads and vector reductions: a pointer off that boundary would fault on the device, so it is refused here.
+template <class... Ptr>
+bool aligned16(Ptr... p) { return ((reinterpret_cast<uintptr_t>(p) | ...) & 15) == 0; }
 
 bool ws_ok(const void* ws, size_t have, size_t need) {
     return need == 0 || (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && have >= need);
@@ -249,6 +256,7 @@ const char* qlka_status_string(int status) {
         case QLKA_ERR_CUDA:              return "a CUDA runtime call failed";
         case QLKA_ERR_UNSUPPORTED:       return "no kernel in this build for these sizes (shifted abs sum: N and n_shifts * M must be <= 16384)";
         case QLKA_ERR_NO_ALLOC_LIMIT:    return "problem needs more scratch than the fixed 32 MiB of the no-allocation entry point; use the workspace variant";
+        case QLKA_ERR_ALIGNMENT:         return "v, g_w, g, out_w, grad_v and the attention output must be 16-byte aligned";
         default:                         return "unknown status";
     }
 }
@@ -271,6 +279,7 @@ static int laplace_forward_impl(const float* q, const float* k, const float* v,
     int st = check_dims(P, D, N, M, C);
     if (st) return st;
     if (!q || !k || !v || !out_w || !out_u) return QLKA_ERR_NULL;
+    if (!aligned16(v, out_w)) return QLKA_ERR_ALIGNMENT;
     LaplaceWs ws(workspace, P, D, N, M, C);
     if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
     const int C4 = round4(C), nseg = P * D;
@@ -345,6 +354,7 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
     int st = check_dims(P, D, N, M, C);
     if (st) return st;
     if (!q || !k || !v || !g_w || !grad_q || !grad_k || !grad_v) return QLKA_ERR_NULL;
+    if (!aligned16(v, g_w, grad_v)) return QLKA_ERR_ALIGNMENT;
     LaplaceBwdWs ws(workspace, P, D, N, M, C);
     if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -425,6 +435,7 @@ int qlka_laplace_attention_forward(const float* q, const float* k, const float* 
     int st = attn_check(B, H, S, D, Dv);
     if (st) return st;
     if (!q || !k || !v || !out) return QLKA_ERR_NULL;
+    if (!aligned16(v, out)) return QLKA_ERR_ALIGNMENT;
     if (!(tau > 0.0f)) return QLKA_ERR_BAD_SHAPE;
     const bool masked = keep != nullptr;
     LaplaceAttnWs ws(workspace, B, H, S, D, Dv, masked);
@@ -496,6 +507,7 @@ int qlka_abs_attention_forward(int kind, const float* q, const float* k, const f
     int st = abs_attn_check(kind, B, H, S, D, Dv);
     if (st) return st;
     if (!q || !k || !v || !out) return QLKA_ERR_NULL;
+    if (!aligned16(v, out)) return QLKA_ERR_ALIGNMENT;
     if (!(tau > 0.0f)) return QLKA_ERR_BAD_SHAPE;
     const bool masked = keep != nullptr, bump = kind == 1;
     AbsAttnWs ws(workspace, B, H, S, D, Dv, masked, bump);
@@ -549,7 +561,7 @@ static int noalloc_scratch(void** out) {
     if (!cached[dev]) {
         void* ptr = nullptr;
         CU(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-        cached[dev] = ptr;      // racing first calls store the same value
+        cached[dev] = ptr;      // racing first calls store the same value (pointer stores are atomic on the hosts this builds for)
     }
     *out = cached[dev];
     return QLKA_OK;
@@ -563,6 +575,8 @@ int qlka_weighted_laplace_sum_forward_noalloc(const float* q, const float* k, co
 {
     int st = check_dims(P, D, N, M, C);
     if (st) return st;
+    if (!q || !k || !v || !out_w || !out_u) return QLKA_ERR_NULL;
+    if (!aligned16(v, out_w)) return QLKA_ERR_ALIGNMENT;
     if (LaplaceWs(nullptr, P, D, N, M, C).bytes > QLKA_NOALLOC_SCRATCH_BYTES) return QLKA_ERR_NO_ALLOC_LIMIT;
     void* scratch = nullptr;
     st = noalloc_scratch(&scratch);
@@ -630,6 +644,7 @@ int qlka_weighted_abs_sum_forward(const float* q, const float* k, const float* v
     if (path < -1 || path > 1) return QLKA_ERR_PATH;
     if (path == 1 && (N > 4096 || M > 4096)) return QLKA_ERR_FUSED_UNAVAILABLE;
     if (!q || !k || !v || !out_w) return QLKA_ERR_NULL;
+    if (!aligned16(v, out_w)) return QLKA_ERR_ALIGNMENT;
     return abs_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C, 0, nullptr, nullptr,
                             reinterpret_cast<cudaStream_t>(stream_));
 }
@@ -654,6 +669,7 @@ int qlka_weighted_abs_sum_shifted_forward(const float* q, const float* k, const 
     if (st) return st;
     if ((long long)n_shifts * M > SMALL_MAX || N > SMALL_MAX) return QLKA_ERR_UNSUPPORTED;
     if (!q || !k || !v || !out_w || !shifts || !weights) return QLKA_ERR_NULL;
+    if (!aligned16(v, out_w)) return QLKA_ERR_ALIGNMENT;
     return abs_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C, n_shifts, shifts, weights,
                             reinterpret_cast<cudaStream_t>(stream_));
 }
@@ -676,6 +692,7 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
     int st = check_dims(P, D, N, M, C);
     if (st) return st;
     if (!q || !k || !v || !g_w || !grad_q || !grad_k || !grad_v) return QLKA_ERR_NULL;
+    if (!aligned16(v, g_w, grad_v)) return QLKA_ERR_ALIGNMENT;
     AbsBwdWs ws(workspace, P, D, N, M, C);
     if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -738,6 +755,7 @@ int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v
     int st = check_dims(P, D, N, M, C);
     if (st) return st;
     if (!q || !k || !v || !g || !out) return QLKA_ERR_NULL;
+    if (!aligned16(v, g)) return QLKA_ERR_ALIGNMENT;
     AbsBwdWs ws(workspace, P, D, N, M, C);
     if (!ws_ok(workspace, workspace_bytes, ws.bytes)) return QLKA_ERR_WORKSPACE;
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);

@@ -32,7 +32,7 @@ namespace qlka {
 enum { LAP_ROWS = 0, LAP_DOT = 1, LAP_BOTH = 2 };
 
 template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS : 1)) laplace_walk(const WalkArgs a)
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) laplace_walk(const WalkArgs a)
 {
     constexpr bool DO_ROWS = EMIT != LAP_DOT, DO_DOT = EMIT != LAP_ROWS;
     constexpr int STREAMS = WALK_THREADS / LPS;

@@ -22,7 +22,7 @@ namespace qlka {
 enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2 };     // BOTH: one walk feeds a row reduction and a dot output
 
 template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? QLKA_WALK_MIN_CTAS : 1)) prefix_walk(const WalkArgs a)
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) prefix_walk(const WalkArgs a)
 {
     constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr int  CW      = LPS * CPL;

@@ -30,17 +30,9 @@
 
 namespace qlka {
 
-#ifndef QLKA_WALK_THREADS
-#define QLKA_WALK_THREADS 256
-#endif
-constexpr int WALK_THREADS = QLKA_WALK_THREADS;
-#ifndef QLKA_RING_DEPTH
-#define QLKA_RING_DEPTH 2
-#endif
-#ifndef QLKA_WALK_MIN_CTAS
-#define QLKA_WALK_MIN_CTAS 2
-#endif
-constexpr int RING_DEPTH   = QLKA_RING_DEPTH;   // blocks in flight: the one in use and RING_DEPTH - 1 prefetched
+constexpr int WALK_THREADS  = 256;
+constexpr int WALK_MIN_CTAS = 2;     // resident CTAs per SM the narrow (4 channels per lane) walks are compiled for
+constexpr int RING_DEPTH    = 2;     // blocks in flight: the one in use and RING_DEPTH - 1 prefetched
 constexpr int RING_AHEAD   = RING_DEPTH - 1;
 constexpr int SX_STRIDE    = 12;     // floats per staged scalar slot: 8 decays / keys and the next four
 constexpr int G_SLOTS      = 8;      // emit-side rows staged per batch (a power of two)

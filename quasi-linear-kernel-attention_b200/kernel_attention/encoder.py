@@ -1,5 +1,5 @@
 """A plain pre-LN transformer encoder whose attention is one of the additive kernels, for end-to-end
-latency and peak-memory measurements of the operators (BASELINE config 4: 12 layers, hidden 768,
+latency and peak-memory measurements of the operators (defaults: 12 layers, hidden 768,
 12 heads of 64, MLP 3072 with GELU, rotary positions, vocabulary 30528, fp32, random weights).
 
 The reference has no such encoder of its own; the block structure follows its pre-LN `EncoderBlock`

@@ -94,6 +94,12 @@ def check_qkv(q, k, v, names="q, k and v"):
     return q.size(0), q.size(1), k.size(2), q.size(2), v.size(2)      # P, D, N, M, C
 
 
+def _aligned(t):
+    """The row matrices must start on a 16-byte boundary (include/qlka.h); a contiguous view at an odd
+    storage offset is copied once instead of being refused, as the reference accepts any contiguous tensor."""
+    return t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format)
+
+
 def _check_like(t, name, shape, ref):
     _check(t.is_cuda and t.device == ref.device, f"{name} must be on q's CUDA device")
     _check(t.dtype == torch.float32, f"{name} must be float32")
@@ -115,6 +121,7 @@ def _stream():
 
 def laplace_forward(q, k, v):
     P, D, N, M, C = dims = check_qkv(q, k, v)
+    v = _aligned(v)
     L = lib()
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_laplace_forward_workspace_bytes, dims, q.device)
@@ -133,6 +140,7 @@ def laplace_forward_noalloc(q, k, v, out_w=None, out_u=None):
     and `out_u` (P, M) to keep this wrapper from allocating too. Raises if the problem needs more
     scratch than the array holds. Calls must not overlap on the GPU (they share the array)."""
     P, D, N, M, C = check_qkv(q, k, v)
+    v = _aligned(v)
     L = lib()
     with torch.cuda.device(q.device):
         if out_w is None:
@@ -237,6 +245,7 @@ def laplace_stage_times(q, k, v, reps=5):
 
 def abs_forward(q, k, v, full, path=-1):
     P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
+    v = _aligned(v)
     L = lib()
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_abs_forward_workspace_bytes, dims, q.device)
@@ -253,6 +262,7 @@ def abs_forward(q, k, v, full, path=-1):
 def abs_shifted_forward(q, k, v, shifts, weights, full=True):
     """sum_s weights[s] * abs_sum(q + shifts[s], k, v) from one sort of the keys: (out_w, out_u or None)."""
     P, D, N, M, C = check_qkv(q, k, v, "q, k, and v")
+    v = _aligned(v)
     ns = len(shifts)
     _check(len(weights) == ns and 1 <= ns <= 4, "shifts and weights must have the same length, 1 to 4")
     L = lib()
@@ -279,6 +289,7 @@ def abs_backward(q, k, v, g_w, g_u=None):
     _check_like(g_w, "g_w", (P, M, C), q)
     if g_u is not None:
         _check_like(g_u, "g_u", (P, M), q)
+    v, g_w = _aligned(v), _aligned(g_w)
     L = lib()
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_abs_backward_workspace_bytes, dims, q.device)
@@ -304,7 +315,7 @@ def fused_attention(kernel, q, k, v, tau, keep=None):
     _check(q.dtype == k.dtype == v.dtype == torch.float32, "q, k, and v must be float32")
     _check(q.dim() == 4 and k.shape == q.shape and v.dim() == 4 and v.shape[:3] == q.shape[:3],
            "expected q, k (B, H, S, D) and v (B, H, S, Dv)")
-    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    q, k, v = q.contiguous(), k.contiguous(), _aligned(v.contiguous())
     B, H, S, D = q.shape
     Dv = v.shape[3]
     if keep is not None:
@@ -343,6 +354,7 @@ def laplace_backward(q, k, v, g_w, g_u=None):
     _check_like(g_w, "g_w", (P, M, C), q)
     if g_u is not None:
         _check_like(g_u, "g_u", (P, M), q)
+    v, g_w = _aligned(v), _aligned(g_w)
     L = lib()
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_laplace_backward_workspace_bytes, dims, q.device)
@@ -361,6 +373,7 @@ def laplace_backward(q, k, v, g_w, g_u=None):
 def sgn_forward(q, k, v, g):
     P, D, N, M, C = dims = check_qkv(q, k, v, "q, k, and v")
     _check_like(g, "g", (P, M, C), q)
+    v, g = _aligned(v), _aligned(g)
     L = lib()
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_sgn_forward_workspace_bytes, dims, q.device)

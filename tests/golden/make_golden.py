@@ -1,8 +1,8 @@
 """Generates the golden vectors in this folder from the reference's own Python code.
 
-Run in a container that has the reference checkout (its path is the argument; the default is in the code below):
+Run in a container that has the reference checkout (its path is the argument, or QLKA_REFERENCE_DIR):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 The reference's `Experiments/kernel_attention/{kernels,attention}.py` are imported
 unchanged; its two CUDA extension packages (which `attention.py` imports at module
@@ -25,7 +25,9 @@ import types
 import numpy as np
 import torch
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("QLKA_REFERENCE_DIR")
+if not ref:
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/reference   (or set QLKA_REFERENCE_DIR)")
 for name in ("weighted_abs_sum", "weighted_laplace_sum"):
     stub = types.ModuleType(name)
     stub.weighted_abs_sum_full = None

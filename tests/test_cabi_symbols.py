@@ -54,7 +54,7 @@ def test_dimension_checks_follow_the_reference(lib):
     assert fwd(None, None, None, None, None, None, 0, 1, 1, 8, 8, 4, 7, None) == 5
     assert fwd(None, None, None, None, None, None, 0, 1, 1, 5000, 8, 4, 1, None) == 6
     assert fwd(None, None, None, None, None, None, 0, 1, 1, 8, 8, 4, -1, None) == 7
-    assert lib.qlka_weighted_laplace_sum_forward(1, 1, 1, 1, 1, None, 0, 1, 1, 8, 8, 4, None) == 8
+    assert lib.qlka_weighted_laplace_sum_forward(16, 16, 16, 16, 16, None, 0, 1, 1, 8, 8, 4, None) == 8
 
 
 def test_workspace_grows_with_the_problem(lib):
@@ -97,8 +97,28 @@ def test_newer_entry_points_check_their_arguments(lib):
     assert lib.qlka_abs_attention_workspace_bytes(0, 1, 1, 6000, 16, 16, 0, ctypes.byref(n)) == 0
     f = lib.qlka_abs_attention_forward
     assert f(0, None, None, None, None, ctypes.c_float(1.0), None, None, 0, 1, 1, 8, 4, 4, None) == 7     # null tensors
-    assert f(0, 1, 1, 1, None, ctypes.c_float(0.0), 1, None, 0, 1, 1, 8, 4, 4, None) == 1                 # tau must be > 0
+    assert f(0, 16, 16, 16, None, ctypes.c_float(0.0), 16, None, 0, 1, 1, 8, 4, 4, None) == 1             # tau must be > 0
     # shifted abs sum and the fixed-scratch Laplace entry refuse what they cannot hold
     assert lib.qlka_abs_shifted_forward_workspace_bytes(1, 1, 100, 6000, 8, 3, ctypes.byref(n)) == 10
     assert lib.qlka_abs_shifted_forward_workspace_bytes(1, 1, 100, 100, 8, 5, ctypes.byref(n)) == 1
     assert lib.qlka_noalloc_scratch_bytes() == 32 << 20
+
+
+def test_row_matrices_must_be_16_byte_aligned(lib):
+    """v, g_w, g, out_w, grad_v and the attention output are moved with 16-byte accesses; a pointer off that
+    boundary is refused with its own status before anything is launched (the checks need no GPU)."""
+    ok, off = 4096, 4096 + 4
+    assert lib.qlka_weighted_laplace_sum_forward(ok, ok, off, ok, ok, None, 0, 1, 1, 8, 8, 4, None) == 12      # v
+    assert lib.qlka_weighted_laplace_sum_forward(ok, ok, ok, off, ok, None, 0, 1, 1, 8, 8, 4, None) == 12      # out_w
+    assert lib.qlka_weighted_laplace_sum_forward(off, off, ok, ok, off, None, 0, 1, 1, 8, 8, 4, None) == 8     # q, k, out_u: float alignment is enough
+    assert lib.qlka_weighted_laplace_sum_forward_noalloc(ok, ok, off, ok, ok, 1, 1, 8, 8, 4, None) == 12
+    assert lib.qlka_weighted_abs_sum_forward(ok, ok, ok, off, None, None, 0, 1, 1, 8, 8, 4, -1, None) == 12
+    bwd = lib.qlka_weighted_abs_sum_backward
+    assert bwd(ok, ok, ok, off, None, ok, ok, ok, None, 0, 1, 1, 8, 8, 4, None) == 12                          # g_w
+    assert bwd(ok, ok, ok, ok, None, ok, ok, off, None, 0, 1, 1, 8, 8, 4, None) == 12                          # grad_v
+    assert bwd(ok, ok, ok, ok, None, off, off, ok, None, 0, 1, 1, 8, 8, 4, None) == 8                          # grad_q, grad_k
+    assert lib.qlka_weighted_laplace_sum_backward(ok, ok, off, ok, None, ok, ok, ok, None, 0, 1, 1, 8, 8, 4, None) == 12
+    assert lib.qlka_weighted_sgn_sum_forward(ok, ok, ok, off, ok, None, 0, 1, 1, 8, 8, 4, None) == 12          # g
+    assert lib.qlka_laplace_attention_forward(ok, ok, ok, None, ctypes.c_float(1.0), off, None, 0, 1, 1, 8, 4, 4, None) == 12
+    assert lib.qlka_abs_attention_forward(0, ok, ok, off, None, ctypes.c_float(1.0), ok, None, 0, 1, 1, 8, 4, 4, None) == 12
+    assert b"16-byte" in lib.qlka_status_string(12)

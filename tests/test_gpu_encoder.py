@@ -1,4 +1,4 @@
-"""The end-to-end encoder harness (BASELINE config 4 shape, shrunk): the add_laplace encoder output equals
+"""The end-to-end encoder harness (the 12-layer pre-LN encoder, shrunk): the add_laplace encoder output equals
 the same network with its attention evaluated by the float64 O(N^2) checker."""
 
 import pytest

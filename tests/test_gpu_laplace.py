@@ -143,3 +143,23 @@ def test_fused_attention_entry(shape, masked):
         qg = q.clone().requires_grad_(True)
         slow = attention(qg, k, v, "add_laplace", 0.5, keep)                      # op-by-op route
     assert rel_err(out, slow.double()) < 1e-5
+
+
+def test_contiguous_view_at_an_odd_storage_offset():
+    """A contiguous v whose storage offset puts it 4 bytes off a 16-byte boundary: the C ABI refuses such a row
+    matrix with its own status (the kernels use 16-byte accesses), the Python operator copies it once instead."""
+    import qlka_native
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs(2, 3, 500, 400, 64, seed=77)
+    store = torch.empty(v.numel() + 1, device="cuda")
+    v_off = store[1:].view_as(v)
+    v_off.copy_(v)
+    assert v_off.is_contiguous() and v_off.data_ptr() % 16 == 4
+    lib = qlka_native.lib()
+    out_w, out_u = torch.empty(2, 400, 64, device="cuda"), torch.empty(2, 400, device="cuda")
+    st = lib.qlka_weighted_laplace_sum_forward_noalloc(q.data_ptr(), k.data_ptr(), v_off.data_ptr(), out_w.data_ptr(),
+                                                       out_u.data_ptr(), 2, 3, 500, 400, 64, torch.cuda.current_stream().cuda_stream)
+    assert st == 12
+    a_w, a_u = weighted_laplace_sum(q, k, v_off)
+    b_w, b_u = weighted_laplace_sum(q, k, v)
+    assert rel_err(a_w, b_w.double()) < 1e-5 and rel_err(a_u, b_u.double()) < 1e-5

@@ -5,7 +5,7 @@ the north star: max|a - b| / max|b| <= 1e-4."""
 import pytest
 import torch
 
-from util import make_inputs, rel_err
+from util import err_stats, make_inputs, make_inputs_cuda, rel_err
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-4
@@ -48,3 +48,56 @@ def test_abs_forward_backward_sgn(ref, shape):
     for mine, theirs in zip(qlka_native.abs_backward(q, k, v, g_w), ref["abs"].weighted_abs_sum_backward(q, k, v, g_w)):
         assert rel_err(mine, theirs.double()) < TOL
     assert rel_err(qlka_native.sgn_forward(q, k, v, g_w), ref["abs"].weighted_sgn_sum_forward(q, k, v, g_w).double()) < TOL
+
+
+# ---- the benchmark configurations at full size, every head compared
+def _close(tag, mine, theirs, tol=TOL):
+    mx, p999 = err_stats(mine, theirs.double())
+    print(f"{tag}: max-norm {mx:.2e}, p99.9 element-wise {p999:.2e}")
+    assert mx < tol, (tag, mx)
+
+
+def test_training_step_configuration_full_size(ref):
+    """weighted_abs_sum forward + backward at B=8, H=12, N=4096, D=Dv=64 (q, k ~ 0.5 N(0,1)), with both upstream
+    gradients: all 96 heads against the reference extension."""
+    import qlka_native
+    q, k, v = make_inputs_cuda(96, 64, 4096, 4096, 64, seed=2, scale=0.5)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    g_w = torch.randn(96, 4096, 64, generator=g, device="cuda")
+    g_u = torch.randn(96, 4096, generator=g, device="cuda")
+    rw, ru = ref["abs"].weighted_abs_sum_full_forward(q, k, v, -1)
+    ow, ou = qlka_native.abs_forward(q, k, v, full=True)
+    _close("c2 out_w", ow, rw)
+    _close("c2 out_u", ou, ru)
+    names = ("grad_q", "grad_k", "grad_v")
+    for name, mine, theirs in zip(names, qlka_native.abs_backward(q, k, v, g_w, g_u), ref["abs"].weighted_abs_sum_full_backward(q, k, v, g_w, g_u)):
+        _close(f"c2 full backward {name}", mine, theirs)
+    for name, mine, theirs in zip(names, qlka_native.abs_backward(q, k, v, g_w), ref["abs"].weighted_abs_sum_backward(q, k, v, g_w)):
+        _close(f"c2 backward {name}", mine, theirs)
+
+
+def test_inference_configuration_full_size(ref):
+    """weighted_laplace_sum forward at B=4, H=12, N=16384, D=Dv=64 (q, k ~ 2 N(0,1)): all 48 heads."""
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs_cuda(48, 64, 16384, 16384, 64, seed=3, scale=2.0)
+    rw, ru = ref["laplace"].weighted_laplace_sum_forward(q, k, v)
+    ow, ou = weighted_laplace_sum(q, k, v)
+    _close("c3 out_w", ow, rw)
+    _close("c3 out_u", ou, ru)
+
+
+def test_long_context_configuration_65536(ref):
+    """B=1, H=16, D=Dv=64, N=M=65536 (q, k ~ N(0,1)), both operators, all heads. 262144 is beyond the
+    reference's length limit (Weighted_Laplace_Sum/csrc/binding.cpp:77-79) and has no counterpart here."""
+    import qlka_native
+    from weighted_laplace_sum import weighted_laplace_sum
+    q, k, v = make_inputs_cuda(16, 64, 65536, 65536, 64, seed=4)
+    rw, ru = ref["laplace"].weighted_laplace_sum_forward(q, k, v)
+    ow, ou = weighted_laplace_sum(q, k, v)
+    _close("c5a laplace out_w", ow, rw, 1e-3)       # dense keys: the fp32 recurrences of either side are ~1e-4 from float64
+    _close("c5a laplace out_u", ou, ru, 1e-3)
+    del rw, ru, ow, ou
+    rw, ru = ref["abs"].weighted_abs_sum_full_forward(q, k, v, -1)
+    ow, ou = qlka_native.abs_forward(q, k, v, full=True)
+    _close("c5a abs out_w", ow, rw)
+    _close("c5a abs out_u", ou, ru)

@@ -43,10 +43,39 @@ def test_matches_workspace_entry_point_on_two_calls_in_a_row():
         assert rel_err(got_u, ref_u.double()) < TOL
 
 
+def test_later_calls_leave_free_device_memory_unchanged():
+    """The one claim of the entry point: once the scratch array exists (the first call on a device
+    materialises it), a call takes no device memory - neither through the CUDA allocator nor
+    through torch's. Outputs are preallocated so that the wrapper allocates nothing either."""
+    import qlka_native
+    lib = qlka_native.lib()
+    q, k, v = make_inputs(2, 8, 1500, 1200, 64, seed=33, scale=2.0)
+    P, D, M = q.shape
+    N, C = k.shape[2], v.shape[2]
+    out_w = torch.empty(P, M, C, device="cuda")
+    out_u = torch.empty(P, M, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        st = lib.qlka_weighted_laplace_sum_forward_noalloc(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(), out_u.data_ptr(), P, D, N, M, C, stream)
+        assert st == 0, lib.qlka_status_string(st)
+        torch.cuda.synchronize()
+
+    call()                                             # set-up call: may materialise the array and load kernels
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.cuda.memory_reserved() == reserved_before
+
+
 def test_refuses_problems_beyond_the_fixed_scratch():
     import qlka_native
     lib = qlka_native.lib()
-    dummy = torch.zeros(4, device="cuda")
+    dummy = torch.zeros(64, device="cuda")
     # B=4, H=12, N=16384, D=64 needs far more than 32 MiB of scratch: refused before any launch
     st = lib.qlka_weighted_laplace_sum_forward_noalloc(
         dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(), dummy.data_ptr(),

@@ -11,6 +11,21 @@
 
 namespace qlka {
 
+// Diagnostic build only (-DQLKA_PHASE_CLOCKS, see phase_clocks_main.cu): thread 0 of every CTA adds the cycles it spent
+// between two marks to a global table, so that the kernel's phases can be weighed against each other.
+#ifdef QLKA_PHASE_CLOCKS
+__device__ unsigned long long g_phase_clocks[16];
+#define PHASE_BEGIN() long long phase_t_ = clock64()
+#define PHASE_MARK(i)                                                                                        \
+    do {                                                                                                     \
+        __syncthreads();                                                                                     \
+        if (threadIdx.x == 0) { const long long t_ = clock64(); atomicAdd(&g_phase_clocks[i], (unsigned long long)(t_ - phase_t_)); phase_t_ = t_; } \
+    } while (0)
+#else
+#define PHASE_BEGIN()
+#define PHASE_MARK(i)
+#endif
+
 // ------------------------------------------------------------------ block radix sort
 // Elements are held in registers, E per thread, in warp-blocked order: the element at
 // array position warp*32*E + s*32 + lane sits in slot s of that lane. One pass ranks each
@@ -273,17 +288,21 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     uint32_t* mstart = a.mstart + (long long)seg * mstride(N);
     float*    su0    = a.su0 ? a.su0 + (long long)seg * (N + 1) : nullptr;
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
+    PHASE_BEGIN();
     // ---- (1) keys
     {
         uint32_t key[E], idx[E];
         load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
+        PHASE_MARK(0);
         block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum);
     }
+    PHASE_MARK(1);
     for (int j = tid; j < NP; j += THREADS) {
         if (j < N) xs[skew(j)] = key2f(skey[j]);
         xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     }
     __syncthreads();
+    PHASE_MARK(2);
     // ---- (2) per-key scalars; my run of keys is [i0, i0 + cntk). The run length is odd so that the
     // strided shared-memory accesses below are bank-conflict free; results leave through a staging
     // buffer (the idle sort buffer) so that the global stores are coalesced.
@@ -355,6 +374,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         }
     }
     __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
+    PHASE_MARK(3);
     // ---- (3) queries: rank, counting sort by rank, records
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
@@ -386,6 +406,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         #pragma unroll
         for (int t = 0; t < QI; t++) rp[s0 + t] = (uint32_t)posq[t];     // number of keys strictly below the query
     }
+    PHASE_MARK(4);
     #pragma unroll
     for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rp[s]], 1u);
     __syncthreads();
@@ -406,6 +427,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         if (m < M) who[rp[s] >> 16] = (uint32_t)m | (rp[s] << 16);
     }
     __syncthreads();
+    PHASE_MARK(5);
     #pragma unroll 4
     for (int pos = tid; pos < M; pos += THREADS) {
         const uint32_t w = who[pos];
@@ -431,6 +453,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)row, (uint32_t)r);
     }
     if (tid == 0) yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu);      // sentinel: a rank no key position has
+    PHASE_MARK(6);
 }
 
 

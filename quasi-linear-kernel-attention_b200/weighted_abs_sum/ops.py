@@ -61,7 +61,7 @@ class _WeightedAbsSumFull(torch.autograd.Function):
         q, k, v = ctx.saved_tensors
         if g_w is None and g_u is None:
             return None, None, None, None
-        if g_u is None:     # out_u unused -> the cheaper plain backward
+        if g_u is None:     # nothing flowed back into the row sums: the native call skips their scalar terms
             grad_q, grad_k, grad_v = _native.abs_backward(q, k, v, g_w.contiguous())
         else:
             if g_w is None:

@@ -86,14 +86,15 @@ int qlka_weighted_laplace_sum_forward_noalloc(const float* q, const float* k, co
                                               int P, int D, int N, int M, int C, qlka_stream_t stream);
 
 /* Diagnostic: the same call, but it waits for completion and reports the device time of the
- * sort/rank kernel and of the walk kernel (CUDA events on `stream`), in milliseconds.
+ * sort/rank kernel, of the first walk pass (with the small fold kernel that follows it) and of the
+ * second, emitting walk pass (CUDA events on `stream`), in milliseconds.
  * The reference has no counterpart; its benchmark times whole calls
  * (Experiments/speed_and_memory/bench.py:83-121). */
 int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v,
                                   float* out_w, float* out_u,
                                   void* workspace, size_t workspace_bytes,
                                   int P, int D, int N, int M, int C, qlka_stream_t stream,
-                                  float* sort_ms, float* walk_ms);
+                                  float* sort_ms, float* pass1_ms, float* pass2_ms);
 
 /* ---- weighted Laplace sum, backward -----------------------------------------------------
  * Gradients of sum(out_w * g_w) + sum(out_u * g_u) (g_u NULL: first term only):

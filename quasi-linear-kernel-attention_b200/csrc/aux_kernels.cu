@@ -29,8 +29,9 @@ __global__ void __launch_bounds__(RS_THREADS) rowstat_kernel(
     const int R, const int C4)
 {
     __shared__ float red_w[RS_THREADS], red_k[RS_THREADS];
-    const int p  = blockIdx.y;
-    const int r0 = blockIdx.x * RS_ROWS, r1 = min(R, r0 + RS_ROWS);
+    const int chunks = (R + RS_ROWS - 1) / RS_ROWS;               // (p rides in blockIdx.x: a grid's y extent stops at 65535)
+    const int p  = blockIdx.x / chunks;
+    const int r0 = (blockIdx.x % chunks) * RS_ROWS, r1 = min(R, r0 + RS_ROWS);
     const int CW = C4 <= 32 ? 32 : (C4 <= 64 ? 64 : 128);
     const int c  = threadIdx.x % CW, lane_r = threadIdx.x / CW, nr = RS_THREADS / CW;
     float aw = 0.0f, ak = 0.0f, as = 0.0f;
@@ -112,8 +113,9 @@ __global__ void __launch_bounds__(256) transpose_scale_kernel(const float* __res
                                                               const int S, const int D, const int H)
 {
     __shared__ float tile[32][33];
-    const int p  = blockIdx.z;
-    const int s0 = blockIdx.x * 32, d0 = blockIdx.y * 32;
+    const int stiles = (S + 31) / 32;
+    const int p  = blockIdx.x / stiles;
+    const int s0 = (blockIdx.x % stiles) * 32, d0 = blockIdx.y * 32;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;       // 32 x 8
     const float* sp = src + (long long)p * S * D;
     float*       dp = dst + (long long)p * D * S;
@@ -228,7 +230,7 @@ cudaError_t launch_abscolsum_d(const float* x, float* out, int P, int D, int L, 
     return cudaGetLastError();
 }
 cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st) {
-    dim3 grid((R + RS_ROWS - 1) / RS_ROWS, P);
+    const unsigned grid = (unsigned)((R + RS_ROWS - 1) / RS_ROWS) * (unsigned)P;
     rowstat_kernel<<<grid, RS_THREADS, 0, st>>>(w, s, wsum, swsum, ssum, R, C4);
     return cudaGetLastError();
 }
@@ -254,7 +256,7 @@ cudaError_t launch_unpad_rows(const float* src, float* dst, long long rows, int 
 }
 
 cudaError_t launch_transpose_scale(const float* src, float* dst, const float* keep, float scale, int P, int S, int D, int H, cudaStream_t st) {
-    dim3 grid((S + 31) / 32, (D + 31) / 32, P);
+    dim3 grid((unsigned)((S + 31) / 32) * (unsigned)P, (D + 31) / 32);
     transpose_scale_kernel<<<grid, 256, 0, st>>>(src, dst, keep, scale, S, D, H);
     return cudaGetLastError();
 }

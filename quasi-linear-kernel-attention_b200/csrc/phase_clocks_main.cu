@@ -61,12 +61,15 @@ int main(int argc, char** argv) {
     CK(cudaEventElapsedTime(&ms, e0, e1));
     unsigned long long clk[16];
     CK(cudaMemcpyFromSymbol(clk, g_phase_clocks, sizeof(clk)));
-    const char* names[7] = {"load keys", "radix sort of the keys (4 passes)", "sorted keys to floats, xperm out", "decays and scalar scans, xval / su out",
-                            "rank search (binary search per query)", "rank histogram, scan, mstart, positions", "records built and written"};
+    // marks in the order the kernel passes them
+    const int   order[9] = {0, 1, 2, 3, 4, 7, 8, 5, 6};
+    const char* names[9] = {"load keys", "radix sort of the keys (4 passes)", "sorted keys to floats, xperm out", "decays and scalar scans, xval / su out",
+                            "bucket index, rank search", "rank histogram, scan, mstart, positions", "scalar side channel (out_u / out_s)",
+                            "values and indices to record positions", "records built and written"};
     double total = 0.0;
-    for (int i = 0; i < 7; i++) total += (double)clk[i];
+    for (int i = 0; i < 9; i++) total += (double)clk[order[i]];
     printf("%d segments of %d keys and %d queries: %.3f ms per launch (instrumented build)\n", nseg, N, M, ms / reps);
-    for (int i = 0; i < 7; i++)
-        printf("  %-44s %6.1f %%  %9.0f cycles per segment\n", names[i], 100.0 * clk[i] / total, (double)clk[i] / ((double)nseg * reps));
+    for (int i = 0; i < 9; i++)
+        printf("  %-44s %6.1f %%  %9.0f cycles per segment\n", names[i], 100.0 * clk[order[i]] / total, (double)clk[order[i]] / ((double)nseg * reps));
     return 0;
 }

@@ -10,10 +10,12 @@ namespace qlka {
 cudaError_t launch_sort_rank_small(const SortArgs& a, cudaStream_t stream);
 cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_t stream);
 size_t      sort_rank_large_scratch_bytes(int nseg, int N, int M);
-cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
-cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream);
+cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream, cudaEvent_t mid);
+cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream);
 int         walk_lanes_per_stream(int C4);
 int         walk_threads();
+int         laplace_agg_stride(int C4);
+int         prefix_agg_stride_host(int C4);
 cudaError_t launch_colsum_d(const float* x, float* out, int P, int D, int L, cudaStream_t st);
 cudaError_t launch_rowstat(const float* w, const float* s, float* wsum, float* swsum, float* ssum, int P, int R, int C4, cudaStream_t st);
 cudaError_t launch_vecsum(const float* x, float* out, int P, int L, cudaStream_t st);
@@ -85,29 +87,33 @@ int sm_count() {
     return cached[dev];
 }
 
-// how a walk over `nseg` segments of N keys is cut into streams, items and CTAs
-struct WalkPlan { int sps, segs, nitems, grid; };
+// How a walk over `nseg` segments of N keys is cut into streams, work items and CTAs. Streams are independent
+// work units (the passes exchange their states through memory), so a segment may be cut into any number of them:
+// more streams until the persistent CTAs of the second pass get about sixteen items each, as long as a stream
+// keeps at least sixteen key blocks (the staging ring needs a few blocks to fill).
+struct WalkPlan { int sps, nitems, grid1, grid2; };
 
 WalkPlan plan_walk(int nseg, int N, int C4) {
     const int lps      = walk_lanes_per_stream(C4);
-    const int streams  = walk_threads() / lps;
-    const int per_sm = C4 <= 64 ? 2 : 1;        // resident walk CTAs per SM (registers and shared memory)
-    const int grid_cap = sm_count() * per_sm;
+    const int streams  = walk_threads() / lps;       // streams per CTA and work item
+    const int sms      = sm_count();
+    const int cap2     = sms * (C4 <= 64 ? 2 : 1);    // resident CTAs of the emitting pass (registers and shared memory)
+    const int cap1     = sms * (C4 <= 64 ? 3 : 1);    // ... and of the lighter first pass
     const int nbk      = nblocks(N);
-    // streams per segment: a divisor of the CTA's stream count; more of them until there are enough items to
-    // balance the persistent CTAs, but at least four key blocks per stream when the segment allows it
+    auto items = [&](long long sps) { return (long long)(((long long)nseg * sps + streams - 1) / streams); };
     int sps = 1;
-    for (int cand = 2; cand <= streams; cand++) {
-        if (streams % cand || cand > nbk || nbk / cand < 4) continue;
-        if ((long long)nseg * sps / streams >= 8LL * grid_cap) break;
-        sps = cand;
-    }
+    while (items(sps) < 16LL * cap2 && nbk / (sps * 2) >= 16 && sps < 4096) sps *= 2;
     WalkPlan w;
     w.sps    = sps;
-    w.segs   = streams / sps;
-    w.nitems = (nseg + w.segs - 1) / w.segs;
-    w.grid   = w.nitems < grid_cap ? w.nitems : grid_cap;
+    w.nitems = (int)items(sps);
+    w.grid1  = w.nitems < cap1 ? w.nitems : cap1;
+    w.grid2  = w.nitems < cap2 ? w.nitems : cap2;
     return w;
+}
+
+// per-stream aggregate table and (Laplace) per-segment checkpoint arrays of a planned walk
+size_t walk_agg_floats(const WalkPlan& w, int nseg, int C4, bool laplace) {
+    return (size_t)nseg * w.sps * (laplace ? laplace_agg_stride(C4) : prefix_agg_stride_host(C4));
 }
 
 // scratch of one sort/rank run over nseg segments of N keys and M queries
@@ -163,7 +169,7 @@ bool ws_ok(const void* ws, size_t have, size_t need) {
 
 // ------------------------------------------------------------------ Laplace forward
 struct LaplaceWs {
-    float* vpad; float* opad; Records rec; float* ckpt; float* wck; WalkPlan plan; size_t bytes;
+    float* vpad; float* opad; Records rec; float* ckpt; float* wck; float* agg; WalkPlan plan; size_t bytes;
     LaplaceWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
@@ -171,15 +177,16 @@ struct LaplaceWs {
         opad = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
         rec.carve(b, nseg, N, M);
         plan = plan_walk(nseg, N, C4);
-        ckpt = b.take<float>((size_t)plan.grid * plan.segs * nblocks(N) * C4);
-        wck  = b.take<float>((size_t)plan.grid * plan.segs * nblocks(N));
+        ckpt = b.take<float>((size_t)nseg * nblocks(N) * C4);
+        wck  = b.take<float>((size_t)nseg * nblocks(N));
+        agg  = b.take<float>(walk_agg_floats(plan, nseg, C4, true));
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
 
 // ------------------------------------------------------------------ Laplace backward
 struct LaplaceBwdWs {
-    float *vpad, *gpad, *gvpad; Records rec; float* ckpt; float* wck; WalkPlan plan_k, plan_q; size_t bytes;
+    float *vpad, *gpad, *gvpad; Records rec; float* ckpt; float* wck; float* agg; WalkPlan plan_k, plan_q; size_t bytes;
     LaplaceBwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
@@ -190,18 +197,18 @@ struct LaplaceBwdWs {
         rec.carve(b, nseg, mx, mx);
         plan_k = plan_walk(nseg, N, C4);        // stream of keys k (grad_q)
         plan_q = plan_walk(nseg, M, C4);        // stream of keys q (grad_v, grad_k)
-        const size_t slots_k = (size_t)plan_k.grid * plan_k.segs * nblocks(N);
-        const size_t slots_q = (size_t)plan_q.grid * plan_q.segs * nblocks(M);
-        const size_t slots   = slots_k > slots_q ? slots_k : slots_q;
+        const size_t slots = (size_t)nseg * nblocks(mx);
         ckpt = b.take<float>(slots * C4);
         wck  = b.take<float>(slots);
+        const size_t agg_k = walk_agg_floats(plan_k, nseg, C4, true), agg_q = walk_agg_floats(plan_q, nseg, C4, true);
+        agg  = b.take<float>(agg_k > agg_q ? agg_k : agg_q);
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
 
 // ------------------------------------------------------------------ abs forward
 struct AbsFwdWs {
-    float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr; WalkPlan plan; size_t bytes;
+    float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr, *agg; WalkPlan plan; size_t bytes;
     AbsFwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
@@ -214,6 +221,7 @@ struct AbsFwdWs {
         ktot  = vsum ? vsum + (size_t)P * C4 : nullptr;
         ksr   = vsum ? ktot + (size_t)P * C4 : nullptr;
         plan  = plan_walk(nseg, N, C4);
+        agg   = b.take<float>(walk_agg_floats(plan, nseg, C4, false));
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
@@ -221,7 +229,8 @@ struct AbsFwdWs {
 // ------------------------------------------------------------------ abs backward / sgn
 struct AbsBwdWs {
     float *vpad, *gpad, *gvpad; Records rec;
-    float *qsumd, *ksumd, *sums /* vsum | gwsum | qtotg | gu_total */;
+    float *qsumd, *ksumd, *sums /* vsum | gwsum | qtotg | gu_total */, *agg;
+    WalkPlan plan_k, plan_q;     // stream of keys k (grad_q, sgn) / stream of keys q (grad_v, grad_k)
     size_t bytes;
     AbsBwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
@@ -234,6 +243,10 @@ struct AbsBwdWs {
         qsumd = b.take<float>((size_t)P * M);
         ksumd = b.take<float>((size_t)P * N);
         sums  = b.take<float>((size_t)P * C4 * 3 + P);
+        plan_k = plan_walk(nseg, N, C4);
+        plan_q = plan_walk(nseg, M, C4);
+        const size_t agg_k = walk_agg_floats(plan_k, nseg, C4, false), agg_q = walk_agg_floats(plan_q, nseg, C4, false);
+        agg   = b.take<float>(agg_k > agg_q ? agg_k : agg_q);
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
@@ -300,9 +313,9 @@ static int laplace_forward_impl(const float* q, const float* k, const float* v,
     if (ev) CU(cudaEventRecord(ev[1], stream));
 
     WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
-    w.ckpt = ws.ckpt; w.wck = ws.wck; w.out = out;
-    CU(launch_laplace_walk(w, EMIT_ROWS, ws.plan.grid, stream));
-    if (ev) CU(cudaEventRecord(ev[2], stream));
+    w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.out = out;
+    CU(launch_laplace_walk(w, EMIT_ROWS, ws.plan.grid1, ws.plan.grid2, stream, ev ? ev[2] : nullptr));
+    if (ev) CU(cudaEventRecord(ev[3], stream));
 
     if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
     return QLKA_OK;
@@ -319,20 +332,21 @@ int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const floa
 int qlka_laplace_forward_stage_ms(const float* q, const float* k, const float* v,
                                   float* out_w, float* out_u, void* workspace, size_t workspace_bytes,
                                   int P, int D, int N, int M, int C, qlka_stream_t stream_,
-                                  float* sort_ms, float* walk_ms)
+                                  float* sort_ms, float* pass1_ms, float* pass2_ms)
 {
-    if (!sort_ms || !walk_ms) return QLKA_ERR_NULL;
-    cudaEvent_t ev[3];
-    for (int i = 0; i < 3; i++) CU(cudaEventCreate(&ev[i]));
+    if (!sort_ms || !pass1_ms || !pass2_ms) return QLKA_ERR_NULL;
+    cudaEvent_t ev[4];
+    for (int i = 0; i < 4; i++) CU(cudaEventCreate(&ev[i]));
     int st = laplace_forward_impl(q, k, v, out_w, out_u, workspace, workspace_bytes, P, D, N, M, C,
                                   reinterpret_cast<cudaStream_t>(stream_), ev);
     if (st == QLKA_OK) {
-        cudaError_t e = cudaEventSynchronize(ev[2]);
+        cudaError_t e = cudaEventSynchronize(ev[3]);
         if (e == cudaSuccess) e = cudaEventElapsedTime(sort_ms, ev[0], ev[1]);
-        if (e == cudaSuccess) e = cudaEventElapsedTime(walk_ms, ev[1], ev[2]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(pass1_ms, ev[1], ev[2]);
+        if (e == cudaSuccess) e = cudaEventElapsedTime(pass2_ms, ev[2], ev[3]);
         if (e != cudaSuccess) { g_last_cuda = (int)e; st = QLKA_ERR_CUDA; }
     }
-    for (int i = 0; i < 3; i++) cudaEventDestroy(ev[i]);
+    for (int i = 0; i < 4; i++) cudaEventDestroy(ev[i]);
     return st;
 }
 
@@ -379,8 +393,8 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
         s.uq = g_u; s.out_s = grad_q;
         CU(launch_sort_rank(s, ws.rec, stream));
         WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
-        w.ckpt = ws.ckpt; w.wck = ws.wck; w.g = grows; w.out_s = grad_q;
-        CU(launch_laplace_walk(w, EMIT_DOT, ws.plan_k.grid, stream));
+        w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.g = grows; w.out_s = grad_q;
+        CU(launch_laplace_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream, nullptr));
     }
     {   // roles swapped: queries k walk the stream q whose rows are g_w (and whose per-key scalar is g_u);
         // the row emission is grad_v, the dot with the v rows is grad_k
@@ -388,8 +402,8 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
         s.us = g_u; s.out_s = grad_k;
         CU(launch_sort_rank(s, ws.rec, stream));
         WalkArgs w = walk_args(ws.rec, ws.plan_q, grows, nseg, D, M, N, C4);
-        w.ckpt = ws.ckpt; w.wck = ws.wck; w.g = vrows; w.out_s = grad_k; w.out = gv;
-        CU(launch_laplace_walk(w, EMIT_BOTH, ws.plan_q.grid, stream));
+        w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.g = vrows; w.out_s = grad_k; w.out = gv;
+        CU(launch_laplace_walk(w, EMIT_BOTH, ws.plan_q.grid1, ws.plan_q.grid2, stream, nullptr));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
     return QLKA_OK;
@@ -416,7 +430,7 @@ struct LaplaceAttnWs {
 
 static int attn_check(int B, int H, int S, int D, int C) {
     if (B <= 0 || H <= 0) return QLKA_ERR_BAD_SHAPE;
-    if ((long long)B * H > 65535) return QLKA_ERR_UNSUPPORTED;
+    if ((long long)B * H > INT_MAX || D > 32 * 65535) return QLKA_ERR_INT32;
     return check_dims(B * H, D, S, S, C);
 }
 
@@ -628,8 +642,8 @@ static int abs_forward_impl(const float* q, const float* k, const float* v, floa
     CU(launch_sort_rank(s, ws.rec, stream));
 
     WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, MQ, C4);
-    w.out = out; w.Mrows = M;
-    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid, stream));
+    w.out = out; w.Mrows = M; w.agg = ws.agg;
+    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid1, ws.plan.grid2, stream));
 
     if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
     return QLKA_OK;
@@ -722,22 +736,20 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
         SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, full ? SCAL_RANK : SCAL_NONE);
         s.uq = g_u;
         CU(launch_sort_rank(s, ws.rec, stream));
-        WalkPlan plan = plan_walk(nseg, N, C4);
-        WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
-        w.g = grows; w.wtotal = vsum; w.out_s = grad_q;
-        CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
+        WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
+        w.g = grows; w.wtotal = vsum; w.out_s = grad_q; w.agg = ws.agg;
+        CU(launch_prefix_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream));
     }
     {   // roles swapped: queries k walk the stream q whose rows are g_w
         SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_ABS, full ? SCAL_PREFIX : SCAL_NONE);
         s.us = g_u; s.us_total = gu_total;
         CU(launch_sort_rank(s, ws.rec, stream));
-        WalkPlan plan = plan_walk(nseg, M, C4);
         // one walk for both: grad_v = abs sum with keys q, weights g_w, evaluated at the keys k (row reductions on
         // top of its rank-1 initial value); grad_k = prefix of g_w rows contracted with v rows (+ the g_u term in e1)
         CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, 1.0f, 0.0f, stream));
-        WalkArgs w = walk_args(ws.rec, plan, grows, nseg, D, M, N, C4);
-        w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k; w.out = gv;
-        CU(launch_prefix_walk(w, EMIT_BOTH, plan.grid, stream));
+        WalkArgs w = walk_args(ws.rec, ws.plan_q, grows, nseg, D, M, N, C4);
+        w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k; w.out = gv; w.agg = ws.agg;
+        CU(launch_prefix_walk(w, EMIT_BOTH, ws.plan_q.grid1, ws.plan_q.grid2, stream));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
     return QLKA_OK;
@@ -774,10 +786,9 @@ int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v
 
     SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, SCAL_NONE);
     CU(launch_sort_rank(s, ws.rec, stream));
-    WalkPlan plan = plan_walk(nseg, N, C4);
-    WalkArgs w = walk_args(ws.rec, plan, vrows, nseg, D, N, M, C4);
-    w.g = grows; w.wtotal = vsum; w.out_s = out; w.sign = -1.0f;
-    CU(launch_prefix_walk(w, EMIT_DOT, plan.grid, stream));
+    WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
+    w.g = grows; w.wtotal = vsum; w.out_s = out; w.sign = -1.0f; w.agg = ws.agg;
+    CU(launch_prefix_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream));
     return QLKA_OK;
 }
 

@@ -68,14 +68,15 @@ struct WalkArgs {
     const float*    xval;
     const uint4*    yrec;
     const uint32_t* mstart;
-    float*          ckpt;     // Laplace: [cta slot][NBK][C4] suffix checkpoints
-    float*          wck;      // Laplace: [cta slot][NBK]
+    float*          ckpt;     // Laplace: [seg][NBK][C4] suffix checkpoints, written by the first pass
+    float*          wck;      // Laplace: [seg][NBK]
+    float*          agg;      // [seg * sps + stream][...] per-stream aggregates of the first pass (layout per walk)
     float*          out;      // emit rows: (P, M, C4), accumulated with vector reductions
     const float*    g;        // emit dot: (P, M, C4) matrix contracted with the walk state
     const float*    wtotal;   // emit dot, prefix walk: (P, C4) column sums of rows
     float*          out_s;    // emit dot: (P, D, M); plain stores in the prefix walk, added to in the Laplace walk
     float           sign;     // emit dot, prefix walk: output scale (+1 gradients, -1 public sgn op)
-    int nseg, D, N, M, C4, sps, nitems;
+    int nseg, D, N, M, C4, sps, nitems;   // sps streams per segment, nitems work items of WALK_THREADS / LPS streams
     int Mrows;                // rows of `out` per p (= M unless the queries are folded)
 };
 

@@ -101,11 +101,18 @@ __device__ __forceinline__ void block_radix_sort(
             base[tid] = pre + incl - tot;
         }
         __syncthreads();
+        // fold the digit starts into the per-warp offsets (every thread's entries share one digit, THREADS being a
+        // multiple of 256), so that the scatter below looks up one table, not two
+        {
+            const uint32_t bd = base[tid & 255];
+            for (int i = tid; i < W * 256; i += THREADS) cnt[i] += bd;
+        }
+        __syncthreads();
 
         #pragma unroll
         for (int s = 0; s < E; s++) {
             const uint32_t d   = (key[s] >> shift) & 255u;
-            const uint32_t dst = base[d] + mycnt[d] + rk[s];
+            const uint32_t dst = mycnt[d] + rk[s];
             skey[dst] = key[s];
             sidx[dst] = (uint16_t)idx[s];
         }
@@ -275,6 +282,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     uint32_t* cnt  = reinterpret_cast<uint32_t*>(wb + 32);          // per-warp digit counters ...
     uint16_t* sidx = reinterpret_cast<uint16_t*>(cnt + W * 256);    // ... and the index payload; together >= 4 * CAP bytes
     float*    su0s = reinterpret_cast<float*>(cnt);                 // Laplace: forward unit scan, once both are idle
+    uint16_t* bst  = sidx + CAP;                                    // bucket index of the rank search, CAP / 4 + 2 entries
 
     const int tid = threadIdx.x;
     const int seg = blockIdx.x;
@@ -376,6 +384,27 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
     PHASE_MARK(3);
     // ---- (3) queries: rank, counting sort by rank, records
+    // The rank search goes through a bucket index over the sorted keys: NB equal-width value buckets between the
+    // smallest and the largest key, bst[b] = number of keys in buckets below b. The bucket of a value is a
+    // monotone function of it, so a query's rank lies in [bst[b], bst[b + 1]] for its own bucket b and the binary
+    // search only covers that range (a handful of keys for smooth key distributions; any distribution stays
+    // correct, a degenerate one just searches a longer range).
+    constexpr int NB = CAP / 4;
+    const float blo = xs[skew(0)];
+    const float bwd = xs[skew(N - 1)] - blo;
+    const float bsc = (bwd > 1e-30f && bwd < 1e30f) ? (float)NB / bwd : 0.0f;
+    auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
+    {
+        const int per = (N + THREADS - 1) / THREADS;
+        const int i0 = min(N, tid * per), i1 = min(N, i0 + per);
+        int prev = i0 > 0 && i0 < N ? bucket(xs[skew(i0 - 1)]) : -1;
+        for (int j = i0; j < i1; j++) {
+            const int b = bucket(xs[skew(j)]);
+            for (int t = prev + 1; t <= b; t++) bst[t] = (uint16_t)j;
+            prev = b;
+        }
+        if (i1 == N && i0 < N) for (int t = prev + 1; t <= NB; t++) bst[t] = (uint16_t)N;
+    }
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();
@@ -383,32 +412,43 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     const float* ysrc = a.y + (long long)seg * MR;
     auto yval = [&](int m) -> float { return a.fold ? ysrc[m % MR] + a.shift[m / MR] : ysrc[m]; };
     uint32_t rp[E];                                   // rank, later rank | position << 16 (both <= 16384)
-    // branch-free binary search, QI queries in flight per thread (the probes are latency bound)
+    // Slot s of a thread is query tid + ((s + rot) mod E) * THREADS with rot the segment index: the D segments of a head
+    // run at the same time and all add into the same out_u row, and with a common visiting order their atomics would
+    // queue up on the same sectors; the rotation spreads them over E different parts of the row.
+    const int rot = seg & (E - 1);
+    auto mq = [&](const int s) -> int { return tid + ((s + rot) & (E - 1)) * THREADS; };
+    // QI searches in flight per thread (the probes are latency bound); the loop runs until the thread's longest is done
     constexpr int QI = E >= 8 ? 8 : 4;
     #pragma unroll
     for (int s0 = 0; s0 < E; s0 += QI) {
-        int   posq[QI];
+        int   lo[QI], hi[QI];
         float yq[QI];
+        bool  open = false;
         #pragma unroll
         for (int t = 0; t < QI; t++) {
-            const int m = tid + (s0 + t) * THREADS;
-            yq[t]   = m < M ? yval(m) : 0.0f;
-            posq[t] = 0;
+            const int m = mq(s0 + t);
+            yq[t] = m < M ? yval(m) : 0.0f;
+            const int b = bucket(yq[t]);
+            lo[t] = bst[b]; hi[t] = bst[b + 1];
+            open |= lo[t] < hi[t];
         }
-        #pragma unroll
-        for (int step = CAP; step >= 1; step >>= 1) {
+        while (open) {
+            open = false;
             #pragma unroll
             for (int t = 0; t < QI; t++) {
-                const int probe = posq[t] + step;
-                if (probe <= N && xs[skew(probe - 1)] < yq[t]) posq[t] = probe;
+                if (lo[t] < hi[t]) {
+                    const int mid = (lo[t] + hi[t]) >> 1;
+                    if (xs[skew(mid)] < yq[t]) lo[t] = mid + 1; else hi[t] = mid;
+                    open |= lo[t] < hi[t];
+                }
             }
         }
         #pragma unroll
-        for (int t = 0; t < QI; t++) rp[s0 + t] = (uint32_t)posq[t];     // number of keys strictly below the query
+        for (int t = 0; t < QI; t++) rp[s0 + t] = (uint32_t)lo[t];       // number of keys strictly below the query
     }
     PHASE_MARK(4);
     #pragma unroll
-    for (int s = 0; s < E; s++) if (tid + s * THREADS < M) atomicAdd(&hist[rp[s]], 1u);
+    for (int s = 0; s < E; s++) if (mq(s) < M) atomicAdd(&hist[rp[s]], 1u);
     __syncthreads();
     block_exclusive_sum<THREADS, E>(hist, N + 1, wsum);
     __syncthreads();
@@ -416,15 +456,65 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     __syncthreads();
     #pragma unroll
     for (int s = 0; s < E; s++)
-        if (tid + s * THREADS < M) rp[s] |= atomicAdd(&hist[rp[s]], 1u) << 16;       // final position of the record
+        if (mq(s) < M) rp[s] |= atomicAdd(&hist[rp[s]], 1u) << 16;       // final position of the record
     __syncthreads();
-    // the histogram is spent: its memory now maps every record position to its query (index | rank << 16),
-    // so that the records can be built and written in position order, as full coalesced lines
-    uint32_t* who = skey;
+    PHASE_MARK(7);
+    // The histogram is spent. Three steps from here, so that every access indexed by the query (its value, the
+    // scalar side inputs, the out_u / out_s updates) is coalesced and every record leaves in position order as
+    // full lines:
+    //   A  each thread, for its own queries (rank and position in registers): the
+    //      scalar side channel, whose atomics and stores are consecutive across the warp; the scan it looks up
+    //      by rank that sits in scratch memory (su1 for Laplace, su0 otherwise) is first copied into the spent
+    //      histogram's shared memory, because scattered 4-byte reads of global memory cost more than all the rest;
+    //   B  the query's value and (index | rank << 16) go to shared memory at the record's position - the value into
+    //      the forward-scan array, which step A was the last to read;
+    //   C  in position order: weights from the two neighbouring keys, record written.
+    const bool lap = a.mode == MODE_LAPLACE;
+    // e^{-gap} for the query weights: one ex2.approx (relative error ~ (2 + 1.2 gap) ulp; these weights enter each
+    // output once, unlike the step decays, which multiply into every prefix state and are taken with expm1)
+    auto wexp = [](const float gap) -> float { return __expf(-gap); };
+    float yv[E];                                      // the thread's query values again, all loads in flight together
     #pragma unroll
     for (int s = 0; s < E; s++) {
-        const int m = tid + s * THREADS;
-        if (m < M) who[rp[s] >> 16] = (uint32_t)m | (rp[s] << 16);
+        const int m = mq(s);
+        yv[s] = m < M ? (a.fold ? __ldg(ysrc + m % MR) + a.shift[m / MR] : __ldg(ysrc + m)) : 0.0f;
+    }
+    if (a.scal == SCAL_UNIT || (SIGNED && a.scal == SCAL_SIGNED)) {
+        float*       suq   = reinterpret_cast<float*>(skey);
+        const float* susrc = lap ? su1 : su0;
+        #pragma unroll 8
+        for (int j = tid; j < N; j += THREADS) suq[j] = susrc[j];
+        __syncthreads();
+        #pragma unroll
+        for (int s = 0; s < E; s++) {
+            const int m = mq(s);
+            if (m >= M) continue;
+            const int   r   = (int)(rp[s] & 0xffffu);
+            const float y   = yv[s];
+            const int   row = a.fold ? m % MR : m;
+            const float wq  = a.fold ? a.wgt[m / MR] : 1.0f;
+            if (lap) {
+                const float t0 = r > 0 ? wexp(y - xs[skew(r - 1)]) * su0s[r - 1] : 0.0f;
+                const float t1 = r < N ? wexp(xs[skew(r)] - y) * suq[r] : 0.0f;
+                if (a.scal == SCAL_UNIT) atomicAdd(a.out_u + (long long)p * MR + row, t0 + t1);
+                else a.out_s[(long long)seg * M + m] = (a.uq ? a.uq[(long long)p * M + m] : 1.0f) * (t1 - t0);
+            } else {
+                atomicAdd(a.out_u + (long long)p * MR + row, wq * 2.0f * (y * (float)r - (r > 0 ? suq[r - 1] : 0.0f)));
+            }
+        }
+    }
+    __syncthreads();
+    PHASE_MARK(8);
+    uint32_t* who  = skey;
+    float*    ypos = su0s;
+    #pragma unroll
+    for (int s = 0; s < E; s++) {
+        const int m = mq(s);
+        if (m < M) {
+            const uint32_t pos = rp[s] >> 16;
+            who[pos]  = (uint32_t)m | (rp[s] << 16);
+            ypos[pos] = yv[s];
+        }
     }
     __syncthreads();
     PHASE_MARK(5);
@@ -432,22 +522,16 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     for (int pos = tid; pos < M; pos += THREADS) {
         const uint32_t w = who[pos];
         const int      m = (int)(w & 0xffffu), r = (int)(w >> 16);
-        const float    y   = yval(m);
+        const float    y   = ypos[pos];
         const int      row = a.fold ? m % MR : m;
         const float    wq  = a.fold ? a.wgt[m / MR] : 1.0f;
         float e0 = 0.0f, e1 = 0.0f;
-        if (a.mode == MODE_LAPLACE) {
-            e0 = r > 0 ? expf(-(y - xs[skew(r - 1)])) : 0.0f;
-            e1 = r < N ? expf(-(xs[skew(r)] - y)) : 0.0f;
-            if (a.scal == SCAL_UNIT)
-                atomicAdd(a.out_u + (long long)p * MR + row, (r > 0 ? e0 * su0s[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
-            else if (SIGNED && a.scal == SCAL_SIGNED)
-                a.out_s[(long long)seg * M + m] = (a.uq ? a.uq[(long long)p * M + m] : 1.0f)
-                                                * ((r < N ? e1 * su1[r] : 0.0f) - (r > 0 ? e0 * su0s[r - 1] : 0.0f));
+        if (lap) {
+            e0 = r > 0 ? wexp(y - xs[skew(r - 1)]) : 0.0f;
+            e1 = r < N ? wexp(xs[skew(r)] - y) : 0.0f;
         } else {
             if (a.mode == MODE_ABS) { e0 = 2.0f * y * wq; e1 = a.rows_coef ? -2.0f * wq : 0.0f; }      // row emission: e0 * PV + e1 * PK
-            if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * MR + row, wq * 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
-            else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
+            if (a.scal == SCAL_RANK)        e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
             else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
         }
         yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)row, (uint32_t)r);
@@ -462,7 +546,8 @@ template <int THREADS, int E, bool SIGNED>
 static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
-    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2;
+    const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2
+                      + (size_t)(CAP / 4 + 8) * 2;
     auto kern = sort_rank_small<THREADS, E, SIGNED>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

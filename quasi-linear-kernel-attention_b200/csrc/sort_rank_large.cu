@@ -6,11 +6,15 @@
 //                    segment, then tile by tile (16384 elements) the stable in-tile ranking of the
 //                    shared-memory sort, a tile-local reorder in shared memory, and run-wise coalesced
 //                    writes to the segment's output buffer at the running digit offsets.
-//   key_scalars      per segment: sorted key values, permutation, per-key decays / key values and the
+//   key_scalars      per segment: sorted key values, permutation, per-key decays / key values, the
 //                    scalar scans (unit column or prefix of a per-key scalar), tile by tile with a
-//                    carried state.
-//   rank_records     per sorted query: rank by binary search in the sorted keys, the record, the
-//                    scalar side channel; then the per-block query starts.
+//                    carried state, and a bucket index over the sorted keys for the rank search.
+//   rank_queries     per query (the queries are never sorted): rank by a bucket lookup and a short binary
+//                    search in the sorted keys, one count into the segment's rank histogram.
+//   scan_starts      per segment: exclusive scan of the rank histogram = first record position of every
+//                    rank; every eighth entry is the block start table of the walk.
+//   place_records    per query: position from an atomic cursor on its rank's entry, the scalar side channel
+//                    (coalesced, it is indexed by the query), the record written at its position.
 //
 // The reference covers these sizes with cub::DeviceSegmentedRadixSort (6-bit digits) for segments
 // above 16384 (Weighted_Laplace_Sum/csrc/sort_utils.cu:62-81) and stops at 131072
@@ -135,8 +139,24 @@ __global__ void __launch_bounds__(LT, 1) seg_radix_pass(
 
 // Sorted keys of every segment -> xs (float, [seg][N]), xperm, xval and the scalar scans su0 / su1.
 // One CTA per segment, tiles of LT * LE keys, each thread a contiguous run of LE keys within the tile.
+// Bucket index of the rank search: LNB(N) equal-width value buckets between the smallest and the largest key of a
+// segment; bst[b] = number of keys in buckets below b, bst[LNB] = N. The bucket of a value is monotone in the value,
+// so the rank of a query lies in [bst[b], bst[b + 1]] for its own bucket b.
+__host__ __device__ inline int       large_nb(int n)      { return n / 4 + 1; }
+__host__ __device__ inline long long large_bstride(int n) { return (long long)large_nb(n) + 3; }
+struct BucketMap {
+    float lo, scale; int nb;
+    __device__ __forceinline__ BucketMap(const float* __restrict__ xs, const int n) {
+        lo = __ldg(xs); nb = large_nb(n);
+        const float width = __ldg(xs + n - 1) - lo;
+        scale = (width > 1e-30f && width < 1e30f) ? (float)nb / width : 0.0f;
+    }
+    __device__ __forceinline__ int operator()(const float v) const { return (int)fminf(fmaxf((v - lo) * scale, 0.0f), (float)(nb - 1)); }
+};
+
 __global__ void __launch_bounds__(LT, 1) key_scalars(
-    const uint32_t* __restrict__ ksorted, const uint32_t* __restrict__ isorted, float* __restrict__ xs_all, const SortArgs a)
+    const uint32_t* __restrict__ ksorted, const uint32_t* __restrict__ isorted, float* __restrict__ xs_all,
+    uint32_t* __restrict__ bst_all, const SortArgs a)
 {
     __shared__ float wa[32], wb[32], carry[2];
     const int       tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -155,15 +175,26 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
         if (j < NP) xperm[j] = j < N ? isorted[j] : 0u;
     }
     __syncthreads();
+    {
+        const BucketMap bucket(xs, N);
+        uint32_t* bst = bst_all + seg * large_bstride(N);
+        for (int j = tid; j < N; j += LT) {
+            const int b = bucket(xs[j]), prev = j > 0 ? bucket(xs[j - 1]) : -1;
+            for (int t = prev + 1; t <= b; t++) bst[t] = (uint32_t)j;
+            if (j == N - 1) for (int t = b + 1; t <= bucket.nb; t++) bst[t] = (uint32_t)N;
+        }
+    }
+    const bool lap = a.mode == MODE_LAPLACE;
     auto dec = [&](int j) -> float { return (j > 0 && j < N) ? decay_of(xs[j] - xs[j - 1]) : 0.0f; };
     if (a.mode != MODE_SGN)
         for (int j = tid; j < NP + KB; j += LT)
-            xval[j] = a.mode == MODE_LAPLACE ? (j < N ? dec(j) : 1.0f) : (j < N ? xs[j] : 0.0f);
+            xval[j] = lap ? (j < N ? dec(j) : 1.0f) : (j < N ? xs[j] : 0.0f);
     if (a.scal != SCAL_UNIT && a.scal != SCAL_PREFIX && a.scal != SCAL_SIGNED) return;
+    __syncthreads();          // the scans read the decays back from xval instead of taking every exponential three times
+    auto dec_at = [&](int j) -> float { return (j > 0 && j < N) ? xval[j] : 0.0f; };
 
     // x_j = A_j x_{j-1} + B_j over the segment, forward (into su0) and, for the Laplace unit column,
     // backward (into su1); a tile at a time with the state carried in shared memory
-    const bool   lap = a.mode == MODE_LAPLACE;
     const float* us  = (a.scal == SCAL_PREFIX || (a.scal == SCAL_SIGNED && a.us)) ? a.us + (long long)p * N : nullptr;
     for (int dir = 0; dir < (lap ? 2 : 1); dir++) {
         if (tid == 0) carry[0] = 0.0f;
@@ -177,7 +208,7 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
                 const long long i = t0 + (long long)tid * LE + k;
                 const int       j = dir ? N - 1 - (int)i : (int)i;
                 if (i < N) {
-                    A[k] = lap ? (dir ? dec(j + 1) : dec(j)) : 1.0f;
+                    A[k] = lap ? (dir ? dec_at(j + 1) : dec_at(j)) : 1.0f;
                     B[k] = us ? us[isorted[j]] : (lap ? 1.0f : xs[j]);
                 } else { A[k] = 1.0f; B[k] = 0.0f; }
                 ca = A[k] * ca; cb = fmaf(A[k], cb, B[k]);
@@ -211,19 +242,67 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
     }
 }
 
-__device__ __forceinline__ int lower_bound_g(const float* __restrict__ a, const int n, const float x) {
-    int lo = 0, hi = n;
-    while (lo < hi) { int mid = (lo + hi) >> 1; if (__ldg(a + mid) < x) lo = mid + 1; else hi = mid; }
-    return lo;
-}
-
-// one thread per sorted query
-__global__ void __launch_bounds__(256) rank_records(
-    const uint32_t* __restrict__ ysorted, const uint32_t* __restrict__ yidx, const float* __restrict__ xs_all, const SortArgs a)
+// ---- queries: rank, count
+__global__ void __launch_bounds__(256) rank_queries(
+    const float* __restrict__ xs_all, const uint32_t* __restrict__ bst_all, uint32_t* __restrict__ rq_all,
+    uint32_t* __restrict__ hist_all, const SortArgs a)
 {
     const int       N = a.N, M = a.M;
-    const long long seg = blockIdx.y, mpd = large_pad(M);
-    const int       m = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned  bps = (unsigned)(M + 1 + 255) / 256;       // blocks per segment (the segment index rides in blockIdx.x:
+    const long long seg = blockIdx.x / bps;                    //  a grid's y extent stops at 65535)
+    const int       m = (int)(blockIdx.x % bps) * 256 + threadIdx.x;
+    if (m >= M) return;
+    const float*    xs  = xs_all + seg * N;
+    const uint32_t* bst = bst_all + seg * large_bstride(N);
+    const BucketMap bucket(xs, N);
+    const float y = a.y[seg * M + m];
+    const int   b = bucket(y);
+    int lo = (int)__ldg(bst + b), hi = (int)__ldg(bst + b + 1);
+    while (lo < hi) { const int mid = (lo + hi) >> 1; if (__ldg(xs + mid) < y) lo = mid + 1; else hi = mid; }
+    rq_all[seg * M + m] = (uint32_t)lo;                         // number of keys strictly below the query
+    atomicAdd(hist_all + seg * (N + 4) + lo, 1u);
+}
+
+// ---- exclusive scan of the rank histogram (N + 1 bins) in place; mstart[b] = start of rank b * KB
+__global__ void __launch_bounds__(LT, 1) scan_starts(uint32_t* __restrict__ hist_all, const SortArgs a)
+{
+    __shared__ uint32_t wsum[32], carry;
+    const int       tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int       N = a.N, NBK = nblocks(N);
+    const long long seg = blockIdx.x;
+    uint32_t* hist = hist_all + seg * (N + 4);
+    uint32_t* ms   = a.mstart + seg * mstride(N);
+    if (tid == 0) { carry = 0; ms[NBK] = (uint32_t)a.M; }
+    __syncthreads();
+    for (int t0 = 0; t0 <= N; t0 += LT * KB) {
+        const int i0 = t0 + tid * KB;                           // a thread's run starts on a block boundary
+        uint32_t c[KB], run = 0;
+        #pragma unroll
+        for (int k = 0; k < KB; k++) { c[k] = i0 + k <= N ? hist[i0 + k] : 0u; run += c[k]; }
+        uint32_t incl = run;
+        #pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const uint32_t t = __shfl_up_sync(FULL, incl, off); if (lane >= off) incl += t; }
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        uint32_t pre = carry + incl - run;
+        for (int w = 0; w < warp; w++) pre += wsum[w];
+        if (i0 <= N) ms[i0 / KB] = pre;                         // i0 / KB < NBK because i0 <= N
+        #pragma unroll
+        for (int k = 0; k < KB; k++) { if (i0 + k <= N) hist[i0 + k] = pre; pre += c[k]; }
+        __syncthreads();
+        if (tid == LT - 1) carry = pre;
+        __syncthreads();
+    }
+}
+
+// ---- records at their positions
+__global__ void __launch_bounds__(256) place_records(
+    const float* __restrict__ xs_all, const uint32_t* __restrict__ rq_all, uint32_t* __restrict__ hist_all, const SortArgs a)
+{
+    const int       N = a.N, M = a.M;
+    const unsigned  bps = (unsigned)(M + 1 + 255) / 256;
+    const long long seg = blockIdx.x / bps;
+    const int       m = (int)(blockIdx.x % bps) * 256 + threadIdx.x;
     if (m > M) return;
     uint4* yrec = a.yrec + seg * (M + 1);
     if (m == M) { yrec[M] = make_uint4(0u, 0u, 0u, 0xffffffffu); return; }
@@ -231,72 +310,64 @@ __global__ void __launch_bounds__(256) rank_records(
     const float* xs  = xs_all + seg * N;
     const float* su0 = a.su0 + seg * (N + 1);
     const float* su1 = a.su1 + seg * (N + 1);
-    const float    y   = key2f(ysorted[seg * mpd + m]);
-    const uint32_t row = yidx[seg * mpd + m];       // (folded queries are not supported on this path; the host refuses them)
-    const int      r   = lower_bound_g(xs, N, y);
+    const float    y   = a.y[seg * M + m];                     // (folded queries are not supported on this path; the host refuses them)
+    const int      r   = (int)rq_all[seg * M + m];
+    const uint32_t pos = atomicAdd(hist_all + seg * (N + 4) + r, 1u);
     float e0 = 0.0f, e1 = 0.0f;
     if (a.mode == MODE_LAPLACE) {
-        e0 = r > 0 ? expf(-(y - xs[r - 1])) : 0.0f;
-        e1 = r < N ? expf(-(xs[r] - y)) : 0.0f;
+        e0 = r > 0 ? __expf(-(y - __ldg(xs + r - 1))) : 0.0f;
+        e1 = r < N ? __expf(-(__ldg(xs + r) - y)) : 0.0f;
         if (a.scal == SCAL_UNIT)
-            atomicAdd(a.out_u + (long long)p * M + row, (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
+            atomicAdd(a.out_u + (long long)p * M + m, (r > 0 ? e0 * su0[r - 1] : 0.0f) + (r < N ? e1 * su1[r] : 0.0f));
         else if (a.scal == SCAL_SIGNED)
-            a.out_s[seg * M + row] = (a.uq ? a.uq[(long long)p * M + row] : 1.0f)
-                                   * ((r < N ? e1 * su1[r] : 0.0f) - (r > 0 ? e0 * su0[r - 1] : 0.0f));
+            a.out_s[seg * M + m] = (a.uq ? a.uq[(long long)p * M + m] : 1.0f)
+                                 * ((r < N ? e1 * su1[r] : 0.0f) - (r > 0 ? e0 * su0[r - 1] : 0.0f));
     } else {
         if (a.mode == MODE_ABS) { e0 = 2.0f * y; e1 = a.rows_coef ? -2.0f : 0.0f; }
-        if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + row, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
-        else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + row] * (2.0f * (float)r - (float)N);
+        if (a.scal == SCAL_UNIT)        atomicAdd(a.out_u + (long long)p * M + m, 2.0f * (y * (float)r - (r > 0 ? su0[r - 1] : 0.0f)));
+        else if (a.scal == SCAL_RANK)   e1 = a.uq[(long long)p * M + m] * (2.0f * (float)r - (float)N);
         else if (a.scal == SCAL_PREFIX) e1 = 2.0f * (r > 0 ? su0[r - 1] : 0.0f) - a.us_total[p];
     }
-    yrec[m] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), row, (uint32_t)r);
+    yrec[pos] = make_uint4(__float_as_uint(e0), __float_as_uint(e1), (uint32_t)m, (uint32_t)r);
 }
 
-// mstart[b] = first record whose rank is >= b * KB
-__global__ void __launch_bounds__(256) block_starts(const SortArgs a)
-{
-    const int       N = a.N, M = a.M, NBK = nblocks(N);
-    const long long seg = blockIdx.y;
-    const int       b = blockIdx.x * blockDim.x + threadIdx.x;
-    if (b > NBK) return;
-    const uint4* yrec = a.yrec + seg * (M + 1);
-    uint32_t*    ms   = a.mstart + seg * mstride(N);
-    if (b == NBK) { ms[b] = (uint32_t)M; return; }
-    const uint32_t want = (uint32_t)(b * KB);
-    int lo = 0, hi = M;
-    while (lo < hi) { int mid = (lo + hi) >> 1; if (__ldg(&yrec[mid].w) < want) lo = mid + 1; else hi = mid; }
-    ms[b] = (uint32_t)lo;
-}
-
-// scratch beyond the records: two ping-pong (key, index) buffers of the padded longer length, and the sorted keys
+// scratch beyond the records: two ping-pong (key, index) buffers of the padded key length, the sorted keys, the bucket
+// index, the rank histogram and the rank of every query
 size_t sort_rank_large_scratch_bytes(int nseg, int N, int M) {
-    const long long mx = large_pad(N > M ? N : M);
-    return (size_t)nseg * mx * 4 * sizeof(uint32_t) + (size_t)nseg * N * sizeof(float) + 1024;
+    const long long np = large_pad(N);
+    return (size_t)nseg * np * 4 * sizeof(uint32_t) + (size_t)nseg * N * sizeof(float)
+         + (size_t)nseg * large_bstride(N) * sizeof(uint32_t) + (size_t)nseg * (N + 4) * sizeof(uint32_t)
+         + (size_t)nseg * M * sizeof(uint32_t) + 1024;
 }
 
 cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_t stream)
 {
-    const long long mx  = large_pad(a.N > a.M ? a.N : a.M);
-    uint32_t* k0 = static_cast<uint32_t*>(scratch);
-    uint32_t* i0 = k0 + (size_t)a.nseg * mx;
-    uint32_t* k1 = i0 + (size_t)a.nseg * mx;
-    uint32_t* i1 = k1 + (size_t)a.nseg * mx;
-    float*    xs = reinterpret_cast<float*>(i1 + (size_t)a.nseg * mx);
+    const long long np = large_pad(a.N);
+    uint32_t* k0   = static_cast<uint32_t*>(scratch);
+    uint32_t* i0   = k0 + (size_t)a.nseg * np;
+    uint32_t* k1   = i0 + (size_t)a.nseg * np;
+    uint32_t* i1   = k1 + (size_t)a.nseg * np;
+    float*    xs   = reinterpret_cast<float*>(i1 + (size_t)a.nseg * np);
+    uint32_t* bst  = reinterpret_cast<uint32_t*>(xs + (size_t)a.nseg * a.N);
+    uint32_t* hist = bst + (size_t)a.nseg * large_bstride(a.N);
+    uint32_t* rq   = hist + (size_t)a.nseg * (a.N + 4);
     const size_t smem = (size_t)LTILE * 8 + (size_t)LW * 1024 + 256 * 4 * 3 + 32 * 4;
     cudaError_t e = cudaFuncSetAttribute(seg_radix_pass, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
+    e = cudaMemsetAsync(hist, 0, sizeof(uint32_t) * (size_t)a.nseg * (a.N + 4), stream);
+    if (e != cudaSuccess) return e;
 
-    auto sort = [&](const float* src, int n) {       // result in (k1, i1), segment stride large_pad(n)
-        seg_radix_pass<<<a.nseg, LT, smem, stream>>>(src, nullptr, nullptr, k0, i0, n, 0, 1);
-        seg_radix_pass<<<a.nseg, LT, smem, stream>>>(src, k0, i0, k1, i1, n, 8, 0);
-        seg_radix_pass<<<a.nseg, LT, smem, stream>>>(src, k1, i1, k0, i0, n, 16, 0);
-        seg_radix_pass<<<a.nseg, LT, smem, stream>>>(src, k0, i0, k1, i1, n, 24, 0);
-    };
-    sort(a.x, a.N);
-    key_scalars<<<a.nseg, LT, 0, stream>>>(k1, i1, xs, a);
-    sort(a.y, a.M);
-    rank_records<<<dim3((a.M + 1 + 255) / 256, a.nseg), 256, 0, stream>>>(k1, i1, xs, a);
-    block_starts<<<dim3((nblocks(a.N) + 1 + 255) / 256, a.nseg), 256, 0, stream>>>(a);
+    // the keys: four 8-bit passes, result in (k1, i1), segment stride large_pad(N)
+    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, nullptr, nullptr, k0, i0, a.N, 0, 1);
+    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k0, i0, k1, i1, a.N, 8, 0);
+    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k1, i1, k0, i0, a.N, 16, 0);
+    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k0, i0, k1, i1, a.N, 24, 0);
+    key_scalars<<<a.nseg, LT, 0, stream>>>(k1, i1, xs, bst, a);
+    // the queries: ranked where they are, ordered by rank with a counting sort
+    const unsigned per_query = (unsigned)((a.M + 1 + 255) / 256) * (unsigned)a.nseg;
+    rank_queries<<<per_query, 256, 0, stream>>>(xs, bst, rq, hist, a);
+    scan_starts<<<a.nseg, LT, 0, stream>>>(hist, a);
+    place_records<<<per_query, 256, 0, stream>>>(xs, rq, hist, a);
     return cudaGetLastError();
 }
 

@@ -9,20 +9,23 @@
 //   LAP_BOTH  the row reduction and the dot from one walk (grad_v and grad_k share stream and queries)
 //
 // Replaces the reference's laplace_chunk / laplace_scan / laplace_walk trio
-// (laplace_kernels.cu:65-127, 134-188, 219-409) with one persistent kernel:
-//   * LPS lanes cooperate on one "stream" (a contiguous run of key blocks of one segment),
-//     each lane owning CPL consecutive channels, so a row is one or two 16-byte copies per
-//     lane and a result is one or two 16-byte vector reductions; lanes never exchange rows.
+// (laplace_kernels.cu:65-127, 134-188, 219-409) with two launches over independent work units:
+//   * a "stream" is a contiguous run of key blocks of one segment; a segment is cut into SPS of them
+//     (any number: the host picks it so that the persistent CTAs stay balanced) and the streams of all
+//     segments are numbered consecutively. LPS lanes cooperate on one stream, each lane owning CPL
+//     consecutive channels, so a row is one or two 16-byte copies per lane and a result is one or two
+//     16-byte vector reductions; lanes never exchange rows. A CTA takes WALK_THREADS / LPS consecutive
+//     streams per work item; nothing couples the streams of a CTA.
 //   * rows, per-key decays and query records reach the lanes through the cp.async staging of
 //     walk_ring.cuh, one block ahead of their use.
-//   * pass 1 walks the stream backwards once: the local suffix state at every block start
-//     goes to a per-CTA checkpoint buffer (L2 resident), the stream's forward and backward
-//     aggregates to shared memory.
-//   * a scan over the SPS streams of a segment (shared memory) gives every stream its
-//     incoming prefix state and incoming suffix state.
-//   * pass 2 walks forward: per block of 8 keys the suffix states are rebuilt in registers
-//     from the next checkpoint, the prefix states overwrite the row registers, and the
-//     block's queries are emitted in rank order.
+//   * laplace_pass1 walks every stream backwards once: the local suffix state at every block start goes
+//     to the segment's checkpoint array, the stream's forward and backward aggregates and the decay
+//     across it to the aggregate table.
+//   * laplace_fold turns the aggregates of a segment's streams into the prefix state entering each stream
+//     and the suffix state entering it from above (serial over the streams, parallel over channels).
+//   * laplace_pass2 walks every stream forward from those states: per
+//     block of 8 keys the suffix states are rebuilt in registers from the next checkpoint, the prefix
+//     states overwrite the row registers, and the block's queries are emitted in rank order.
 // The rows are therefore gathered twice (the reference gathers them three times) and every
 // exponential was already taken by the sort/rank kernel.
 #include "walk_ring.cuh"
@@ -31,51 +34,179 @@ namespace qlka {
 
 enum { LAP_ROWS = 0, LAP_DOT = 1, LAP_BOTH = 2 };
 
-template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) laplace_walk(const WalkArgs a)
+// floats per stream in the aggregate table: forward aggregate | backward aggregate | decay forward, decay backward, pad
+__host__ __device__ inline int lap_agg_stride(int C4) { return 2 * C4 + 4; }
+
+
+template <int LPS, int CPL>
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 3 : 1)) laplace_pass1(const WalkArgs a)
 {
-    constexpr bool DO_ROWS = EMIT != LAP_DOT, DO_DOT = EMIT != LAP_ROWS;
     constexpr int STREAMS = WALK_THREADS / LPS;
-    constexpr int CW      = LPS * CPL;               // channel capacity of a stream
     extern __shared__ __align__(16) float4 smem[];
-    float4* ring  = smem;                                                    // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
-    uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());   // [STREAMS][RING_DEPTH][LPS]
-    float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);       // [STREAMS][RING_DEPTH][SX_STRIDE]
-    float4* g_area = reinterpret_cast<float4*>(sx_all + STREAMS * RING_DEPTH * SX_STRIDE);   // dot emissions only: [G_SLOTS][CPL/4][WALK_THREADS]
-    // stream aggregates live in the ring's memory between the two passes
-    float (*sF)[CW] = reinterpret_cast<float (*)[CW]>(ring);                 // forward aggregate  -> incoming prefix state
-    float (*sB)[CW] = sF + STREAMS;                                          // backward aggregate -> incoming suffix state
-    __shared__ float sAF[STREAMS], sAB[STREAMS];     // total decay across the stream (forward / backward)
+    float4* ring   = smem;                                                   // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
+    float*  sx_all = reinterpret_cast<float*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());   // [STREAMS][RING_DEPTH][SX_STRIDE]
 
     const int tid = threadIdx.x;
-    const int st  = tid / LPS;                       // stream slot in this CTA
-    const int ln  = tid % LPS;
-    const int c0  = ln * CPL;
-    const int SPS = a.sps, SEGS = STREAMS / SPS;
-    const int sl  = st / SPS, s = st % SPS;          // segment slot, stream index within the segment
-    const int N = a.N, M = a.M, C4 = a.C4;
+    const int st  = tid / LPS, ln = tid % LPS, c0 = ln * CPL;
+    const int SPS = a.sps;
+    const int N = a.N, C4 = a.C4;
     const int NBK = nblocks(N), NP = npad(N);
     const bool lane_on = c0 < C4;
     const int  c0l     = lane_on ? c0 : 0;           // idle lanes shadow lane 0's loads and store nothing
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
+    const long long nstreams = (long long)a.nseg * SPS;
+
+    Feeder<LPS, CPL> f;
+    f.ring_s = smem_u32(ring + tid);
+    f.qs_s   = 0;                                  // no query records in this pass
+    f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = a.M; f.ln = ln; f.with_x = true; f.with_q = false;
+
+    for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
+        const long long g  = (long long)item * STREAMS + st;         // this stream, in the numbering over all segments
+        const bool      on_s = g < nstreams;
+        const long long gg = on_s ? g : 0;
+        const int  sg = (int)(gg / SPS), s = (int)(gg - (long long)sg * SPS);
+        const int  p  = sg / a.D;
+        const bool on = on_s && lane_on;
+        int b0, b1;
+        stream_blocks(s, SPS, NBK, b0, b1);
+        const int nblk = on_s ? b1 - b0 : 0;
+
+        f.xperm = a.xperm + (long long)sg * NP;
+        f.xval  = a.xval + (long long)sg * xstride(N);
+        f.rows  = a.rows + (long long)p * N * C4 + c0l;
+        float* ck = a.ckpt + (long long)sg * NBK * C4 + c0l;
+        float* wk = a.wck + (long long)sg * NBK;
+
+        Vec<CPL> Rl, F;
+        Rl.zero(); F.zero();
+        float w = 1.0f, wprev = 1.0f;
+        const float a_j1 = (on_s && b1 < NBK) ? __ldg(f.xval + b1 * KB) : 0.0f;   // decay from the next stream's first key
+        __syncwarp(gmask);                         // every lane has left the previous item's slots
+        f.prologue(b1 - 1, -1, nblk);
+        int cur = 0;
+        for (int t = 0; t < nblk; t++) {
+            const int b = b1 - 1 - t, j0 = b * KB;
+            __syncwarp(gmask);                     // every lane is done with the slot refilled below
+            f.step(t, cur, b1 - 1, -1, nblk);
+            __syncwarp(gmask);
+            float av[KB + 1];
+            f.read_scalars(cur, av);
+            Vec<CPL> v[KB];
+            f.read_rows(cur, j0, v);
+            #pragma unroll
+            for (int i = KB - 1; i >= 0; i--) {
+                #pragma unroll
+                for (int c = 0; c < CPL; c += 2) {
+                    fma2(F.x[c], F.x[c + 1], w, w, v[i].x[c], v[i].x[c + 1], F.x[c], F.x[c + 1]);
+                    fma2(Rl.x[c], Rl.x[c + 1], av[i + 1], av[i + 1], Rl.x[c], Rl.x[c + 1], v[i].x[c], v[i].x[c + 1]);
+                }
+                wprev = w;
+                w *= av[i];
+            }
+            if (on) {                              // (streaming stores: the second pass reads them long after, once)
+                #pragma unroll
+                for (int c = 0; c < CPL; c += 4)
+                    __stcs(reinterpret_cast<float4*>(ck + (long long)b * C4 + c), make_float4(Rl.x[c], Rl.x[c + 1], Rl.x[c + 2], Rl.x[c + 3]));
+            }
+            if (ln == 0) wk[b] = wprev * a_j1;
+            cur = ring_next(cur);
+        }
+        cp_async_wait<0>();                        // (the trailing empty groups)
+        if (on_s) {
+            float* ag = a.agg + g * lap_agg_stride(C4);
+            if (lane_on) {
+                #pragma unroll
+                for (int c = 0; c < CPL; c += 4) {
+                    *reinterpret_cast<float4*>(ag + c0 + c)      = make_float4(F.x[c], F.x[c + 1], F.x[c + 2], F.x[c + 3]);
+                    *reinterpret_cast<float4*>(ag + C4 + c0 + c) = make_float4(Rl.x[c], Rl.x[c + 1], Rl.x[c + 2], Rl.x[c + 3]);
+                }
+            }
+            if (ln == 0) { ag[2 * C4] = w; ag[2 * C4 + 1] = wprev * a_j1; }
+        }
+    }
+}
+
+// Between the passes: per segment and channel, the aggregates of the SPS streams become the states entering each
+// stream - in place, forward aggregate -> prefix state before the stream (L = decay * L + aggregate over the earlier
+// streams), backward aggregate -> suffix state after it. One thread per (segment, channel), serial over the streams.
+__global__ void __launch_bounds__(256) laplace_fold(float* __restrict__ agg, const int nseg, const int SPS, const int C4)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)nseg * C4) return;
+    const int sg = (int)(i / C4), c = (int)(i - (long long)sg * C4);
+    const int AGS = lap_agg_stride(C4);
+    float* ag = agg + (long long)sg * SPS * AGS;
+    constexpr int CH = 16;                     // streams per chunk: their loads are issued together, then the serial part
+    float L = 0.0f;
+    for (int t0 = 0; t0 < SPS; t0 += CH) {
+        float fv[CH], af[CH];
+        #pragma unroll
+        for (int k = 0; k < CH; k++) {
+            const float* at = ag + (long long)min(t0 + k, SPS - 1) * AGS;
+            fv[k] = at[c]; af[k] = at[2 * C4];
+        }
+        #pragma unroll
+        for (int k = 0; k < CH; k++) {
+            if (t0 + k < SPS) { ag[(long long)(t0 + k) * AGS + c] = L; L = fmaf(af[k], L, fv[k]); }
+        }
+    }
+    float R = 0.0f;
+    for (int t0 = SPS - 1; t0 >= 0; t0 -= CH) {
+        float bv[CH], ab[CH];
+        #pragma unroll
+        for (int k = 0; k < CH; k++) {
+            const float* at = ag + (long long)max(t0 - k, 0) * AGS;
+            bv[k] = at[C4 + c]; ab[k] = at[2 * C4 + 1];
+        }
+        #pragma unroll
+        for (int k = 0; k < CH; k++) {
+            if (t0 - k >= 0) { ag[(long long)(t0 - k) * AGS + C4 + c] = R; R = fmaf(ab[k], R, bv[k]); }
+        }
+    }
+}
+
+template <int LPS, int CPL, int EMIT>
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) laplace_pass2(const WalkArgs a)
+{
+    constexpr bool DO_ROWS = EMIT != LAP_DOT, DO_DOT = EMIT != LAP_ROWS;
+    constexpr int STREAMS = WALK_THREADS / LPS;
+    extern __shared__ __align__(16) float4 smem[];
+    float4* ring   = smem;                                                   // [RING_DEPTH][KB][CPL/4][WALK_THREADS]
+    uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());   // [STREAMS][RING_DEPTH][LPS]
+    float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);       // [STREAMS][RING_DEPTH][SX_STRIDE]
+    float4* g_area = reinterpret_cast<float4*>(sx_all + STREAMS * RING_DEPTH * SX_STRIDE);   // dot emissions only: [G_SLOTS][CPL/4][WALK_THREADS]
+
+    const int tid = threadIdx.x;
+    const int st  = tid / LPS, ln = tid % LPS, c0 = ln * CPL;
+    const int SPS = a.sps;
+    const int N = a.N, M = a.M, C4 = a.C4;
+    const int NBK = nblocks(N), NP = npad(N);
+    const bool lane_on = c0 < C4;
+    const int  c0l     = lane_on ? c0 : 0;
+    const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
+    const long long nstreams = (long long)a.nseg * SPS;
+    const int AGS = lap_agg_stride(C4);
 
     Feeder<LPS, CPL> f;
     f.ring_s = smem_u32(ring + tid);
     f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
-    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = M; f.ln = ln; f.with_x = true;
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = M; f.ln = ln; f.with_x = true; f.with_q = true;
     f.g_s = smem_u32(g_area + tid);
 
-    // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
+    // static round-robin over the work items (an atomic work counter was measured 10 % slower)
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
-        const int  seg    = item * SEGS + sl;
-        const bool seg_on = seg < a.nseg;
-        const bool on     = seg_on && lane_on;
-        const int  sg     = seg_on ? seg : 0;
-        const int  p      = sg / a.D;
-        const int  b0     = seg_on ? (int)((long long)s * NBK / SPS) : 0;
-        const int  b1     = seg_on ? (int)((long long)(s + 1) * NBK / SPS) : 0;
-        const int  nblk   = b1 - b0;
+        const long long g  = (long long)item * STREAMS + st;
+        const bool      on_s = g < nstreams;
+        const long long gg = on_s ? g : 0;
+        const int  sg = (int)(gg / SPS), s = (int)(gg - (long long)sg * SPS);
+        const int  p  = sg / a.D;
+        const bool on = on_s && lane_on;
+        int b0, b1;
+        stream_blocks(s, SPS, NBK, b0, b1);
+        const int nblk = on_s ? b1 - b0 : 0;
 
         f.xperm  = a.xperm + (long long)sg * NP;
         f.xval   = a.xval + (long long)sg * xstride(N);
@@ -83,83 +214,27 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
         f.mstart = a.mstart + (long long)sg * mstride(N);
         f.yrec   = a.yrec + (long long)sg * (M + 1);
         float*          out   = DO_ROWS ? a.out + (long long)p * a.Mrows * C4 + c0l : nullptr;
-        const float*    g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
+        const float*    g_    = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
         float*          out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
-        f.grows = g;
-        const long long slot = (long long)blockIdx.x * SEGS + sl;
-        float*          ck   = a.ckpt + slot * NBK * C4 + c0l;
-        float*          wk   = a.wck + slot * NBK;
+        f.grows = g_;
+        const float* ck = a.ckpt + (long long)sg * NBK * C4 + c0l;
+        const float* wk = a.wck + (long long)sg * NBK;
 
-        // ---------------- pass 1: backward over the stream
-        Vec<CPL> Rl, F;
-        Rl.zero(); F.zero();
-        float w = 1.0f, wprev = 1.0f;
-        const float a_j1 = (seg_on && b1 < NBK) ? __ldg(f.xval + b1 * KB) : 0.0f;   // decay from the next stream's first key
-        {
-            f.with_q = false;
-            f.prologue(b1 - 1, -1, nblk);
-            int cur = 0;
-            for (int t = 0; t < nblk; t++) {
-                const int b = b1 - 1 - t, j0 = b * KB;
-                __syncwarp(gmask);                     // every lane is done with the slot refilled below
-                f.step(t, cur, b1 - 1, -1, nblk);
-                __syncwarp(gmask);
-                float av[KB + 1];
-                f.read_scalars(cur, av);
-                Vec<CPL> v[KB];
-                f.read_rows(cur, j0, v);
-                #pragma unroll
-                for (int i = KB - 1; i >= 0; i--) {
-                    #pragma unroll
-                    for (int c = 0; c < CPL; c += 2) {
-                        fma2(F.x[c], F.x[c + 1], w, w, v[i].x[c], v[i].x[c + 1], F.x[c], F.x[c + 1]);
-                        fma2(Rl.x[c], Rl.x[c + 1], av[i + 1], av[i + 1], Rl.x[c], Rl.x[c + 1], v[i].x[c], v[i].x[c + 1]);
-                    }
-                    wprev = w;
-                    w *= av[i];
-                }
-                if (on) {
-                    #pragma unroll
-                    for (int c = 0; c < CPL; c += 4)
-                        *reinterpret_cast<float4*>(ck + (long long)b * C4 + c) = make_float4(Rl.x[c], Rl.x[c + 1], Rl.x[c + 2], Rl.x[c + 3]);
-                }
-                if (seg_on && ln == 0) wk[b] = wprev * a_j1;
-                cur = ring_next(cur);
-            }
-        }
-        __syncthreads();        // every thread has left the ring: its memory now holds the aggregates
-        #pragma unroll
-        for (int c = 0; c < CPL; c++) { sF[st][c0 + c] = F.x[c]; sB[st][c0 + c] = Rl.x[c]; }
-        if (ln == 0) { sAF[st] = w; sAB[st] = wprev * a_j1; }
-        __syncthreads();
-
-        // ---------------- scan over the streams of each segment
-        for (int i = tid; i < SEGS * CW; i += WALK_THREADS) {
-            const int g = i / CW, c = i % CW;
-            float L = 0.0f;
-            for (int t = 0; t < SPS; t++) {
-                const int q = g * SPS + t;
-                float fv = sF[q][c];
-                sF[q][c] = L;
-                L = fmaf(sAF[q], L, fv);
-            }
-            float R = 0.0f;
-            for (int t = SPS - 1; t >= 0; t--) {
-                const int q = g * SPS + t;
-                float bb = sB[q][c];
-                sB[q][c] = R;
-                R = fmaf(sAB[q], R, bb);
-            }
-        }
-        __syncthreads();
+        // ---------------- incoming prefix and suffix state (laplace_fold left them in the aggregate table)
         Vec<CPL> L, Rin;
-        #pragma unroll
-        for (int c = 0; c < CPL; c++) { L.x[c] = sF[st][c0 + c]; Rin.x[c] = sB[st][c0 + c]; }
-        __syncthreads();        // aggregates are in registers: the ring may be refilled
-
-        // ---------------- pass 2: forward with emission
         {
-            f.with_q = true;
+            const float* ag = a.agg + gg * AGS + c0l;
+            #pragma unroll
+            for (int c = 0; c < CPL; c += 4) {
+                const float4 fv = ldg4(ag + c), bv = ldg4(ag + C4 + c);
+                L.x[c] = fv.x; L.x[c + 1] = fv.y; L.x[c + 2] = fv.z; L.x[c + 3] = fv.w;
+                Rin.x[c] = bv.x; Rin.x[c + 1] = bv.y; Rin.x[c + 2] = bv.z; Rin.x[c + 3] = bv.w;
+            }
+        }
+
+        // ---------------- forward with emission
+        {
+            __syncwarp(gmask);                         // every lane has left the previous item's slots
             f.prologue(b0, 1, nblk);
             // checkpoint of the block after the current one, fetched one iteration early
             Vec<CPL> cnext; cnext.zero();
@@ -169,7 +244,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                     wnext = wk[bn];
                     #pragma unroll
                     for (int c = 0; c < CPL; c += 4) {
-                        const float4 t = *reinterpret_cast<const float4*>(ck + (long long)bn * C4 + c);
+                        const float4 t = __ldcs(reinterpret_cast<const float4*>(ck + (long long)bn * C4 + c));
                         cnext.x[c] = t.x; cnext.x[c + 1] = t.y; cnext.x[c + 2] = t.z; cnext.x[c + 3] = t.w;
                     }
                 }
@@ -236,7 +311,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                 }
                 // the block's queries, in rank order
                 auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record
-                    const float* gr = g + (size_t)rec.z * C4;
+                    const float* gr = g_ + (size_t)rec.z * C4;
                     #pragma unroll
                     for (int c = 0; c < CPL; c += 4) {
                         const float4 t4 = lane_on ? ldg4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -334,25 +409,32 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                 cur = ring_next(cur);
             }
         }
-        __syncthreads();        // the ring and the aggregates are rewritten by the next item
+        cp_async_wait<0>();
     }
 }
 
 template <int LPS, int CPL, int EMIT>
-static cudaError_t launch_lap(const WalkArgs& a, int grid, cudaStream_t stream) {
-    auto kern = laplace_walk<LPS, CPL, EMIT>;
-    const size_t smem = walk_smem_bytes<LPS, CPL>() + (EMIT != LAP_ROWS ? g_area_bytes<CPL>() : 0);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static cudaError_t launch_lap(const WalkArgs& a, int grid1, int grid2, cudaStream_t stream, cudaEvent_t mid) {
+    auto k1 = laplace_pass1<LPS, CPL>;
+    auto k2 = laplace_pass2<LPS, CPL, EMIT>;
+    const size_t smem1 = pass1_smem_bytes<LPS, CPL>();
+    const size_t smem2 = walk_smem_bytes<LPS, CPL>() + (EMIT != LAP_ROWS ? g_area_bytes<CPL>() : 0);
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (e != cudaSuccess) return e;
-    kern<<<grid, WALK_THREADS, smem, stream>>>(a);
+    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (e != cudaSuccess) return e;
+    k1<<<grid1, WALK_THREADS, smem1, stream>>>(a);
+    laplace_fold<<<(unsigned)(((long long)a.nseg * a.C4 + 255) / 256), 256, 0, stream>>>(a.agg, a.nseg, a.sps, a.C4);
+    if (mid) { e = cudaEventRecord(mid, stream); if (e != cudaSuccess) return e; }
+    k2<<<grid2, WALK_THREADS, smem2, stream>>>(a);
     return cudaGetLastError();
 }
 
 template <int EMIT>
-static cudaError_t launch_lap_c(const WalkArgs& a, int grid, cudaStream_t stream) {
-    if (a.C4 <= 32)  return launch_lap<8, 4, EMIT>(a, grid, stream);
-    if (a.C4 <= 64)  return launch_lap<16, 4, EMIT>(a, grid, stream);
-    if (a.C4 <= 128) return launch_lap<16, 8, EMIT>(a, grid, stream);
+static cudaError_t launch_lap_c(const WalkArgs& a, int grid1, int grid2, cudaStream_t stream, cudaEvent_t mid) {
+    if (a.C4 <= 32)  return launch_lap<8, 4, EMIT>(a, grid1, grid2, stream, mid);
+    if (a.C4 <= 64)  return launch_lap<16, 4, EMIT>(a, grid1, grid2, stream, mid);
+    if (a.C4 <= 128) return launch_lap<16, 8, EMIT>(a, grid1, grid2, stream, mid);
     return cudaErrorInvalidValue;
 }
 
@@ -360,11 +442,16 @@ static cudaError_t launch_lap_c(const WalkArgs& a, int grid, cudaStream_t stream
 int walk_lanes_per_stream(int C4) { return C4 <= 32 ? 8 : 16; }
 int walk_threads() { return WALK_THREADS; }
 
-// emit: 0 = row reductions (the forward sum), 1 = dot, 2 = both
-cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream) {
-    if (emit == LAP_ROWS) return launch_lap_c<LAP_ROWS>(a, grid, stream);
-    if (emit == LAP_DOT)  return launch_lap_c<LAP_DOT>(a, grid, stream);
-    if (emit == LAP_BOTH) return launch_lap_c<LAP_BOTH>(a, grid, stream);
+int laplace_agg_stride(int C4) { return lap_agg_stride(C4); }
+// resident CTAs per SM of the two passes (what the host sizes their grids with)
+int laplace_pass_ctas_per_sm(int C4, int pass) { return C4 <= 64 ? (pass == 1 ? 3 : WALK_MIN_CTAS) : 1; }
+
+// emit: 0 = row reductions (the forward sum), 1 = dot, 2 = both; grid1 / grid2: CTAs of the two passes;
+// mid: optional event recorded between the first pass (with the fold) and the second
+cudaError_t launch_laplace_walk(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream, cudaEvent_t mid) {
+    if (emit == LAP_ROWS) return launch_lap_c<LAP_ROWS>(a, grid1, grid2, stream, mid);
+    if (emit == LAP_DOT)  return launch_lap_c<LAP_DOT>(a, grid1, grid2, stream, mid);
+    if (emit == LAP_BOTH) return launch_lap_c<LAP_BOTH>(a, grid1, grid2, stream, mid);
     return cudaErrorInvalidValue;
 }
 

@@ -12,20 +12,130 @@
 //              output element, plain stores.
 //
 // Same thread mapping and staging as the Laplace walk (LPS lanes per stream, CPL channels per
-// lane, SPS streams per segment, persistent CTAs, cp.async ring). Pass 1 sums each stream's
-// rows, a shared-memory scan turns the sums into each stream's incoming prefix, pass 2 walks
-// forward and emits. With one stream per segment pass 1 and the scan are skipped.
+// lane, SPS independent streams per segment numbered over all segments, persistent CTAs, cp.async
+// ring). The first launch sums each stream's rows into an aggregate table, a small kernel turns the
+// table into exclusive prefix sums over each segment's streams, the last launch walks every stream
+// forward from its incoming prefix and emits. With one stream per segment only the last one runs.
 #include "walk_ring.cuh"
 
 namespace qlka {
 
 enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2 };     // BOTH: one walk feeds a row reduction and a dot output
 
+// floats per stream in the aggregate table: sum of the stream's rows | sum of key * row
+__host__ __device__ inline int prefix_agg_stride(int C4) { return 2 * C4; }
+
+
+// First launch (only with more than one stream per segment): every stream sums its rows (and key * row).
+template <int LPS, int CPL, bool WITH_K>
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? 3 : 1)) prefix_pass1(const WalkArgs a)
+{
+    constexpr int STREAMS = WALK_THREADS / LPS;
+    extern __shared__ __align__(16) float4 smem[];
+    float4* ring   = smem;
+    float*  sx_all = reinterpret_cast<float*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
+
+    const int tid = threadIdx.x;
+    const int st  = tid / LPS, ln = tid % LPS, c0 = ln * CPL;
+    const int SPS = a.sps;
+    const int N = a.N, C4 = a.C4;
+    const int NBK = nblocks(N), NP = npad(N);
+    const bool lane_on = c0 < C4;
+    const int  c0l     = lane_on ? c0 : 0;
+    const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
+    const long long nstreams = (long long)a.nseg * SPS;
+
+    Feeder<LPS, CPL> f;
+    f.ring_s = smem_u32(ring + tid);
+    f.qs_s   = 0;
+    f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = a.M; f.ln = ln; f.with_x = WITH_K; f.with_q = false;
+
+    for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
+        const long long g  = (long long)item * STREAMS + st;
+        const bool      on_s = g < nstreams;
+        const long long gg = on_s ? g : 0;
+        const int  sg = (int)(gg / SPS), s = (int)(gg - (long long)sg * SPS);
+        const int  p  = sg / a.D;
+        int b0, b1;
+        stream_blocks(s, SPS, NBK, b0, b1);
+        const int nblk = on_s ? b1 - b0 : 0;
+
+        f.xperm = a.xperm + (long long)sg * NP;
+        f.xval  = WITH_K ? a.xval + (long long)sg * xstride(N) : nullptr;
+        f.rows  = a.rows + (long long)p * N * C4 + c0l;
+
+        Vec<CPL> PV, PK;
+        PV.zero(); PK.zero();
+        __syncwarp(gmask);
+        f.prologue(b0, 1, nblk);
+        int cur = 0;
+        for (int t = 0; t < nblk; t++) {
+            const int b = b0 + t, j0 = b * KB;
+            __syncwarp(gmask);
+            f.step(t, cur, b0, 1, nblk);
+            float kv[KB + 1];
+            if (WITH_K) {
+                __syncwarp(gmask);
+                f.read_scalars(cur, kv);
+            }
+            Vec<CPL> v[KB];
+            f.read_rows(cur, j0, v);
+            #pragma unroll
+            for (int i = 0; i < KB; i++) {
+                #pragma unroll
+                for (int c = 0; c < CPL; c += 2) {
+                    add2(PV.x[c], PV.x[c + 1], PV.x[c], PV.x[c + 1], v[i].x[c], v[i].x[c + 1]);
+                    if (WITH_K) fma2(PK.x[c], PK.x[c + 1], kv[i], kv[i], v[i].x[c], v[i].x[c + 1], PK.x[c], PK.x[c + 1]);
+                }
+            }
+            cur = ring_next(cur);
+        }
+        cp_async_wait<0>();
+        if (on_s && lane_on) {
+            float* ag = a.agg + g * prefix_agg_stride(C4) + c0;
+            #pragma unroll
+            for (int c = 0; c < CPL; c += 4) {
+                *reinterpret_cast<float4*>(ag + c) = make_float4(PV.x[c], PV.x[c + 1], PV.x[c + 2], PV.x[c + 3]);
+                if (WITH_K) *reinterpret_cast<float4*>(ag + C4 + c) = make_float4(PK.x[c], PK.x[c + 1], PK.x[c + 2], PK.x[c + 3]);
+            }
+        }
+    }
+}
+
+// Between the launches: per segment and channel, exclusive prefix sums of the stream aggregates, in place.
+__global__ void __launch_bounds__(256) prefix_fold(float* __restrict__ agg, const int nseg, const int SPS, const int C4, const int with_k)
+{
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)nseg * C4) return;
+    const int sg = (int)(i / C4), c = (int)(i - (long long)sg * C4);
+    const int AGS = prefix_agg_stride(C4);
+    float* ag = agg + (long long)sg * SPS * AGS;
+    constexpr int CH = 16;                     // streams per chunk: their loads are issued together, then the serial part
+    float pv = 0.0f, pk = 0.0f;
+    for (int t0 = 0; t0 < SPS; t0 += CH) {
+        float v[CH], k[CH];
+        #pragma unroll
+        for (int j = 0; j < CH; j++) {
+            const float* at = ag + (long long)min(t0 + j, SPS - 1) * AGS;
+            v[j] = at[c]; k[j] = with_k ? at[C4 + c] : 0.0f;
+        }
+        #pragma unroll
+        for (int j = 0; j < CH; j++) {
+            if (t0 + j < SPS) {
+                float* at = ag + (long long)(t0 + j) * AGS;
+                at[c] = pv; pv += v[j];
+                if (with_k) { at[C4 + c] = pk; pk += k[j]; }
+            }
+        }
+    }
+}
+
+// Last launch: the walk with emission, every stream starting from its incoming prefix sums.
 template <int LPS, int CPL, int EMIT>
-__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) prefix_walk(const WalkArgs a)
+__global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) prefix_pass2(const WalkArgs a)
 {
     constexpr int  STREAMS = WALK_THREADS / LPS;
-    constexpr int  CW      = LPS * CPL;
     constexpr bool WITH_K  = EMIT != EMIT_DOT;
     constexpr bool DO_ROWS = EMIT != EMIT_DOT, DO_DOT = EMIT != EMIT_ROWS;
     extern __shared__ __align__(16) float4 smem[];
@@ -33,36 +143,36 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
     uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
     float*  sx_all = reinterpret_cast<float*>(qs_all + STREAMS * RING_DEPTH * LPS);
     float4* g_area = reinterpret_cast<float4*>(sx_all + STREAMS * RING_DEPTH * SX_STRIDE);     // dot emissions only
-    float (*sV)[CW] = reinterpret_cast<float (*)[CW]>(ring);     // stream sums, in the ring's memory between the passes
-    float (*sK)[CW] = sV + STREAMS;
 
     const int tid = threadIdx.x;
     const int st  = tid / LPS, ln = tid % LPS, c0 = ln * CPL;
-    const int SPS = a.sps, SEGS = STREAMS / SPS;
-    const int sl  = st / SPS, s = st % SPS;
+    const int SPS = a.sps;
     const int N = a.N, M = a.M, C4 = a.C4;
     const int NBK = nblocks(N), NP = npad(N);
     const bool lane_on = c0 < C4;
     const int  c0l     = lane_on ? c0 : 0;
     const unsigned gmask = (LPS == 32) ? FULL : (((1u << LPS) - 1u) << ((tid & 31) & ~(LPS - 1)));
+    const long long nstreams = (long long)a.nseg * SPS;
+    const int AGS = prefix_agg_stride(C4);
 
     Feeder<LPS, CPL> f;
     f.ring_s = smem_u32(ring + tid);
     f.qs_s   = smem_u32(qs_all + st * RING_DEPTH * LPS);
     f.sx_s   = smem_u32(sx_all + st * RING_DEPTH * SX_STRIDE);
-    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = M; f.ln = ln; f.with_x = WITH_K;
+    f.row_bytes = (uint32_t)C4 * 4u; f.N = N; f.M = M; f.ln = ln; f.with_x = WITH_K; f.with_q = true;
     f.g_s = smem_u32(g_area + tid);
 
-    // static round-robin over the work items (an atomic work counter was measured 10 % slower here)
+    // static round-robin over the work items (an atomic work counter was measured 10 % slower)
     for (int item = blockIdx.x; item < a.nitems; item += gridDim.x) {
-        const int  seg    = item * SEGS + sl;
-        const bool seg_on = seg < a.nseg;
-        const bool on     = seg_on && lane_on;
-        const int  sg     = seg_on ? seg : 0;
-        const int  p      = sg / a.D;
-        const int  b0     = seg_on ? (int)((long long)s * NBK / SPS) : 0;
-        const int  b1     = seg_on ? (int)((long long)(s + 1) * NBK / SPS) : 0;
-        const int  nblk   = b1 - b0;
+        const long long g  = (long long)item * STREAMS + st;
+        const bool      on_s = g < nstreams;
+        const long long gg = on_s ? g : 0;
+        const int  sg = (int)(gg / SPS), s = (int)(gg - (long long)sg * SPS);
+        const int  p  = sg / a.D;
+        const bool on = on_s && lane_on;
+        int b0, b1;
+        stream_blocks(s, SPS, NBK, b0, b1);
+        const int nblk = on_s ? b1 - b0 : 0;
 
         f.xperm  = a.xperm + (long long)sg * NP;
         f.xval   = WITH_K ? a.xval + (long long)sg * xstride(N) : nullptr;
@@ -72,58 +182,17 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
 
         Vec<CPL> PV, PK;
         PV.zero(); PK.zero();
-
-        if (SPS > 1) {
-            // ---------------- pass 1: stream sums
-            f.with_q = false;
-            f.prologue(b0, 1, nblk);
-            int cur = 0;
-            for (int t = 0; t < nblk; t++) {
-                const int b = b0 + t, j0 = b * KB;
-                __syncwarp(gmask);
-                f.step(t, cur, b0, 1, nblk);
-                float kv[KB + 1];
+        if (SPS > 1) {          // incoming prefix sums (prefix_fold left them in the aggregate table)
+            const float* ag = a.agg + gg * AGS + c0l;
+            #pragma unroll
+            for (int c = 0; c < CPL; c += 4) {
+                const float4 pv = ldg4(ag + c);
+                PV.x[c] = pv.x; PV.x[c + 1] = pv.y; PV.x[c + 2] = pv.z; PV.x[c + 3] = pv.w;
                 if (WITH_K) {
-                    __syncwarp(gmask);
-                        f.read_scalars(cur, kv);
-                }
-                Vec<CPL> v[KB];
-                f.read_rows(cur, j0, v);
-                #pragma unroll
-                for (int i = 0; i < KB; i++) {
-                    #pragma unroll
-                    for (int c = 0; c < CPL; c += 2) {
-                        add2(PV.x[c], PV.x[c + 1], PV.x[c], PV.x[c + 1], v[i].x[c], v[i].x[c + 1]);
-                        if (WITH_K) fma2(PK.x[c], PK.x[c + 1], kv[i], kv[i], v[i].x[c], v[i].x[c + 1], PK.x[c], PK.x[c + 1]);
-                    }
-                }
-                cur = ring_next(cur);
-            }
-            __syncthreads();        // every thread has left the ring: its memory now holds the sums
-            #pragma unroll
-            for (int c = 0; c < CPL; c++) {
-                sV[st][c0 + c] = PV.x[c];
-                if (WITH_K) sK[st][c0 + c] = PK.x[c];
-            }
-            __syncthreads();
-            for (int i = tid; i < SEGS * CW; i += WALK_THREADS) {
-                const int g = i / CW, c = i % CW;
-                float accv = 0.0f, acck = 0.0f;
-                for (int t = 0; t < SPS; t++) {
-                    const int q = g * SPS + t;
-                    float fv = sV[q][c];
-                    sV[q][c] = accv;
-                    accv += fv;
-                    if (WITH_K) { float fk = sK[q][c]; sK[q][c] = acck; acck += fk; }
+                    const float4 pk = ldg4(ag + C4 + c);
+                    PK.x[c] = pk.x; PK.x[c + 1] = pk.y; PK.x[c + 2] = pk.z; PK.x[c + 3] = pk.w;
                 }
             }
-            __syncthreads();
-            #pragma unroll
-            for (int c = 0; c < CPL; c++) {
-                PV.x[c] = sV[st][c0 + c];
-                if (WITH_K) PK.x[c] = sK[st][c0 + c];
-            }
-            __syncthreads();        // prefixes are in registers: the ring may be refilled
         }
 
         // emit-side constants
@@ -137,13 +206,13 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
             }
         }
         float*       out   = DO_ROWS ? a.out + (long long)p * a.Mrows * C4 + c0l : nullptr;
-        const float* g     = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
+        const float* g_    = DO_DOT ? a.g + (long long)p * M * C4 + c0l : nullptr;
         float*       out_s = DO_DOT ? a.out_s + (long long)sg * M : nullptr;
-        f.grows = g;
+        f.grows = g_;
 
         // ---------------- pass 2: forward with emission
         {
-            f.with_q = true;
+            __syncwarp(gmask);                         // every lane has left the previous item's slots
             f.prologue(b0, 1, nblk);
             int cur = 0;
             for (int t = 0; t < nblk; t++) {
@@ -184,7 +253,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                     }
                 }
                 auto load_g = [&](const uint4 rec, Vec<CPL>& gq) {      // the emit-side row slice of a record
-                    const float* gr = g + (size_t)rec.z * C4;
+                    const float* gr = g_ + (size_t)rec.z * C4;
                     #pragma unroll
                     for (int c = 0; c < CPL; c += 4) {
                         const float4 t4 = lane_on ? ldg4(gr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -282,33 +351,45 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                 cur = ring_next(cur);
             }
         }
-        __syncthreads();
+        cp_async_wait<0>();
     }
 }
 
 template <int LPS, int CPL, int EMIT>
-static cudaError_t launch_pw(const WalkArgs& a, int grid, cudaStream_t stream) {
-    auto kern = prefix_walk<LPS, CPL, EMIT>;
-    const size_t smem = walk_smem_bytes<LPS, CPL>() + (EMIT != EMIT_ROWS ? g_area_bytes<CPL>() : 0);
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+static cudaError_t launch_pw(const WalkArgs& a, int grid1, int grid2, cudaStream_t stream) {
+    constexpr bool WITH_K = EMIT != EMIT_DOT;
+    auto k1 = prefix_pass1<LPS, CPL, WITH_K>;
+    auto k2 = prefix_pass2<LPS, CPL, EMIT>;
+    const size_t smem1 = pass1_smem_bytes<LPS, CPL>();
+    const size_t smem2 = walk_smem_bytes<LPS, CPL>() + (EMIT != EMIT_ROWS ? g_area_bytes<CPL>() : 0);
+    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
     if (e != cudaSuccess) return e;
-    kern<<<grid, WALK_THREADS, smem, stream>>>(a);
+    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
+    if (e != cudaSuccess) return e;
+    if (a.sps > 1) {                                                   // (a lone stream per segment has nothing before it)
+        k1<<<grid1, WALK_THREADS, smem1, stream>>>(a);
+        prefix_fold<<<(unsigned)(((long long)a.nseg * a.C4 + 255) / 256), 256, 0, stream>>>(a.agg, a.nseg, a.sps, a.C4, WITH_K ? 1 : 0);
+    }
+    k2<<<grid2, WALK_THREADS, smem2, stream>>>(a);
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid, cudaStream_t stream) {
+int prefix_agg_stride_host(int C4) { return prefix_agg_stride(C4); }
+
+// grid1 / grid2: CTAs of the two launches
+cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream) {
     if (emit == EMIT_ROWS) {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_ROWS>(a, grid, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_ROWS>(a, grid, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_ROWS>(a, grid, stream);
+        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_ROWS>(a, grid1, grid2, stream);
+        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_ROWS>(a, grid1, grid2, stream);
+        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_ROWS>(a, grid1, grid2, stream);
     } else if (emit == EMIT_DOT) {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_DOT>(a, grid, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_DOT>(a, grid, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_DOT>(a, grid, stream);
+        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_DOT>(a, grid1, grid2, stream);
+        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_DOT>(a, grid1, grid2, stream);
+        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_DOT>(a, grid1, grid2, stream);
     } else {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_BOTH>(a, grid, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_BOTH>(a, grid, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_BOTH>(a, grid, stream);
+        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_BOTH>(a, grid1, grid2, stream);
+        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_BOTH>(a, grid1, grid2, stream);
+        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_BOTH>(a, grid1, grid2, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -117,6 +117,10 @@ template <int LPS, int CPL> __host__ __device__ constexpr size_t walk_smem_bytes
     return ring_bytes<CPL>() + (size_t)(WALK_THREADS / LPS) * RING_DEPTH * LPS * sizeof(uint4)
          + (size_t)(WALK_THREADS / LPS) * RING_DEPTH * SX_STRIDE * sizeof(float);
 }
+// a first pass stages rows and per-key scalars only: row ring | scalar slots
+template <int LPS, int CPL> __host__ __device__ constexpr size_t pass1_smem_bytes() {
+    return ring_bytes<CPL>() + (size_t)(WALK_THREADS / LPS) * RING_DEPTH * SX_STRIDE * sizeof(float);
+}
 // the emit-side row area of the dot emissions follows: [G_SLOTS][CPL/4][WALK_THREADS] x 16 B
 template <int CPL> __host__ __device__ constexpr size_t g_area_bytes() { return (size_t)G_SLOTS * (CPL / 4) * WALK_THREADS * 16; }
 
@@ -265,6 +269,12 @@ struct Feeder {
         av[8] = a2.x;
     }
 };
+
+// the key blocks [b0, b1) that stream s of the SPS streams of a segment owns (NBK blocks per segment)
+__device__ __forceinline__ void stream_blocks(const int s, const int SPS, const int NBK, int& b0, int& b1) {
+    b0 = (int)((long long)s * NBK / SPS);
+    b1 = (int)((long long)(s + 1) * NBK / SPS);
+}
 
 __device__ __forceinline__ int ring_next(const int cur) { return cur == RING_DEPTH - 1 ? 0 : cur + 1; }
 

@@ -49,7 +49,7 @@ def lib():
         L.qlka_abs_attention_forward.restype = _i
         L.qlka_abs_attention_forward.argtypes = [_i] + [_vp] * 4 + [ctypes.c_float] + [_vp] + [_vp, _sz] + [_i] * 5 + [_vp]
         L.qlka_laplace_forward_stage_ms.restype = _i
-        L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 2
+        L.qlka_laplace_forward_stage_ms.argtypes = [_vp] * 5 + [_vp, _sz] + [_i] * 5 + [_vp] + [ctypes.POINTER(ctypes.c_float)] * 3
         L.qlka_noalloc_scratch_bytes.restype = _sz
         L.qlka_weighted_laplace_sum_forward_noalloc.restype = _i
         L.qlka_weighted_laplace_sum_forward_noalloc.argtypes = [_vp] * 5 + [_i] * 5 + [_vp]
@@ -222,25 +222,24 @@ class HostPipeline:
 
 
 def laplace_stage_times(q, k, v, reps=5):
-    """Diagnostic: median device time (ms) of the sort/rank kernel and of the walk kernel."""
+    """Diagnostic: median device time (ms) of the sort/rank kernel, of the first walk pass (with its fold kernel)
+    and of the second, emitting pass; `walk_ms` is the sum of the two passes."""
     P, D, N, M, C = dims = check_qkv(q, k, v)
     L = lib()
-    sort_ms, walk_ms = [], []
+    rows = []
     with torch.cuda.device(q.device):
         ws, n = _workspace(L.qlka_laplace_forward_workspace_bytes, dims, q.device)
         out_w = torch.empty(P, M, C, dtype=torch.float32, device=q.device)
         out_u = torch.empty(P, M, dtype=torch.float32, device=q.device)
         for _ in range(reps):
-            a, b = ctypes.c_float(0), ctypes.c_float(0)
+            a, b, c = ctypes.c_float(0), ctypes.c_float(0), ctypes.c_float(0)
             st = L.qlka_laplace_forward_stage_ms(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_w.data_ptr(), out_u.data_ptr(),
-                                                 ws.data_ptr(), n, P, D, N, M, C, _stream(), ctypes.byref(a), ctypes.byref(b))
+                                                 ws.data_ptr(), n, P, D, N, M, C, _stream(), ctypes.byref(a), ctypes.byref(b), ctypes.byref(c))
             if st:
                 _raise(st)
-            sort_ms.append(a.value)
-            walk_ms.append(b.value)
-    sort_ms.sort()
-    walk_ms.sort()
-    return {"sort_rank_ms": sort_ms[len(sort_ms) // 2], "walk_ms": walk_ms[len(walk_ms) // 2]}
+            rows.append((a.value, b.value, c.value))
+    med = [sorted(col)[len(col) // 2] for col in zip(*rows)]
+    return {"sort_rank_ms": med[0], "walk_pass1_ms": med[1], "walk_pass2_ms": med[2], "walk_ms": med[1] + med[2]}
 
 
 def abs_forward(q, k, v, full, path=-1):

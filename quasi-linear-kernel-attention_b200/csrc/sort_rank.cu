@@ -266,10 +266,18 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 // cursor), which also yields mstart for free; the records are then built in position order. Queries of
 // equal rank come out in arbitrary order,
 // which the walk does not care about.
-// SIGNED builds the SCAL_SIGNED side channel in (a separate instance keeps its registers out of the others).
-template <int THREADS, int E, bool SIGNED>
+// The kernel is compiled in four variants, so that each carries only the code of its own case (the whole kernel
+// runs once per segment, straight through: instruction fetch is its most frequent stall, and dead branches cost):
+//   VAR_LAP         Laplace records, optional unit-column side channel
+//   VAR_LAP_SIGNED  Laplace records with the SCAL_SIGNED side channel (its scans run through shared memory)
+//   VAR_ABS         abs / sgn records, the queries as given
+//   VAR_ABS_FOLD    abs records over folded (shifted, weighted) query copies
+enum SortVariant : int { VAR_LAP = 0, VAR_LAP_SIGNED = 1, VAR_ABS = 2, VAR_ABS_FOLD = 3 };
+
+template <int THREADS, int E, int VAR>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const SortArgs a)
 {
+    constexpr bool LAP = VAR == VAR_LAP || VAR == VAR_LAP_SIGNED, SIGNED = VAR == VAR_LAP_SIGNED, FOLD = VAR == VAR_ABS_FOLD;
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -327,24 +335,30 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
             for (int j = tid; j < N; j += THREADS) dst[j] = stage[j];
         };
         float dk[R + 1];                                          // dk[k] = decay a_{i0+k} = exp(-(k_j - k_{j-1})), a_0 = 0, a_N = 0
-        if (a.mode == MODE_LAPLACE) {
+        if (LAP) {
+            // the step decays in key order: to xval (coalesced) and to the staging buffer, from where every thread
+            // picks up the R + 1 of its run (a rolled loop: the exponential is a long instruction sequence)
+            #pragma unroll 2
+            for (int j = tid; j < N; j += THREADS) {
+                const float d = j > 0 ? decay_of(xs[skew(j)] - xs[skew(j - 1)]) : 0.0f;
+                stage[j] = d;
+                xval[j]  = d;
+            }
+            for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
+            __syncthreads();
             #pragma unroll
             for (int k = 0; k <= R; k++) {
                 const int j = i0 + k;
-                dk[k] = (k <= cntk && j > 0 && j < N) ? decay_of(xs[skew(j)] - xs[skew(j - 1)]) : 0.0f;
+                dk[k] = (k <= cntk && j < N) ? stage[j] : 0.0f;
             }
             float bx[R];
-            #pragma unroll
-            for (int k = 0; k < R; k++) bx[k] = dk[k];
-            flush(bx, xval);
-            for (int j = N + tid; j < NP + KB; j += THREADS) xval[j] = 1.0f;
             if (SIGNED && a.scal == SCAL_SIGNED) {
                 // su0[j] = sum_{i<=j} exp(-(k_j - k_i)) u_i,  su1[j] = sum_{i>=j} exp(-(k_i - k_j)) u_i with u the per-key scalar
                 // (all ones without one). The scalars wait in the staging buffer, every thread touching only its own run,
                 // because su0s overwrites the index payload; the backward scan runs in place there and leaves through it.
                 {
                     const float* us = a.us ? a.us + (long long)p * N : nullptr;
-                    __syncthreads();                  // the staging buffer may still be drained by the flush above
+                    __syncthreads();                  // every thread has picked its decays out of the staging buffer
                     #pragma unroll
                     for (int k = 0; k < R; k++) if (k < cntk) stage[i0 + k] = us ? us[sidx[i0 + k]] : 1.0f;
                 }
@@ -408,9 +422,9 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();
-    const int    MR   = a.fold ? a.fold : M;          // distinct query values (and output rows) per segment
+    const int    MR   = FOLD ? a.fold : M;            // distinct query values (and output rows) per segment
     const float* ysrc = a.y + (long long)seg * MR;
-    auto yval = [&](int m) -> float { return a.fold ? ysrc[m % MR] + a.shift[m / MR] : ysrc[m]; };
+    auto yval = [&](int m) -> float { return FOLD ? ysrc[m % MR] + a.shift[m / MR] : ysrc[m]; };
     uint32_t rp[E];                                   // rank, later rank | position << 16 (both <= 16384)
     // Slot s of a thread is query tid + ((s + rot) mod E) * THREADS with rot the segment index: the D segments of a head
     // run at the same time and all add into the same out_u row, and with a common visiting order their atomics would
@@ -469,7 +483,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     //   B  the query's value and (index | rank << 16) go to shared memory at the record's position - the value into
     //      the forward-scan array, which step A was the last to read;
     //   C  in position order: weights from the two neighbouring keys, record written.
-    const bool lap = a.mode == MODE_LAPLACE;
+    constexpr bool lap = LAP;
     // e^{-gap} for the query weights: one ex2.approx (relative error ~ (2 + 1.2 gap) ulp; these weights enter each
     // output once, unlike the step decays, which multiply into every prefix state and are taken with expm1)
     auto wexp = [](const float gap) -> float { return __expf(-gap); };
@@ -477,7 +491,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     #pragma unroll
     for (int s = 0; s < E; s++) {
         const int m = mq(s);
-        yv[s] = m < M ? (a.fold ? __ldg(ysrc + m % MR) + a.shift[m / MR] : __ldg(ysrc + m)) : 0.0f;
+        yv[s] = m < M ? (FOLD ? __ldg(ysrc + m % MR) + a.shift[m / MR] : __ldg(ysrc + m)) : 0.0f;
     }
     if (a.scal == SCAL_UNIT || (SIGNED && a.scal == SCAL_SIGNED)) {
         float*       suq   = reinterpret_cast<float*>(skey);
@@ -491,8 +505,8 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
             if (m >= M) continue;
             const int   r   = (int)(rp[s] & 0xffffu);
             const float y   = yv[s];
-            const int   row = a.fold ? m % MR : m;
-            const float wq  = a.fold ? a.wgt[m / MR] : 1.0f;
+            const int   row = FOLD ? m % MR : m;
+            const float wq  = FOLD ? a.wgt[m / MR] : 1.0f;
             if (lap) {
                 const float t0 = r > 0 ? wexp(y - xs[skew(r - 1)]) * su0s[r - 1] : 0.0f;
                 const float t1 = r < N ? wexp(xs[skew(r)] - y) * suq[r] : 0.0f;
@@ -523,8 +537,8 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         const uint32_t w = who[pos];
         const int      m = (int)(w & 0xffffu), r = (int)(w >> 16);
         const float    y   = ypos[pos];
-        const int      row = a.fold ? m % MR : m;
-        const float    wq  = a.fold ? a.wgt[m / MR] : 1.0f;
+        const int      row = FOLD ? m % MR : m;
+        const float    wq  = FOLD ? a.wgt[m / MR] : 1.0f;
         float e0 = 0.0f, e1 = 0.0f;
         if (lap) {
             e0 = r > 0 ? wexp(y - xs[skew(r - 1)]) : 0.0f;
@@ -542,13 +556,13 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
 
 
 
-template <int THREADS, int E, bool SIGNED>
+template <int THREADS, int E, int VAR>
 static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2
                       + (size_t)(CAP / 4 + 8) * 2;
-    auto kern = sort_rank_small<THREADS, E, SIGNED>;
+    auto kern = sort_rank_small<THREADS, E, VAR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     kern<<<a.nseg, THREADS, smem, stream>>>(a);
@@ -557,7 +571,9 @@ static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
 
 template <int THREADS, int E>
 static cudaError_t launch_one(const SortArgs& a, cudaStream_t stream) {
-    return a.scal == SCAL_SIGNED ? launch_inst<THREADS, E, true>(a, stream) : launch_inst<THREADS, E, false>(a, stream);
+    if (a.mode == MODE_LAPLACE)
+        return a.scal == SCAL_SIGNED ? launch_inst<THREADS, E, VAR_LAP_SIGNED>(a, stream) : launch_inst<THREADS, E, VAR_LAP>(a, stream);
+    return a.fold ? launch_inst<THREADS, E, VAR_ABS_FOLD>(a, stream) : launch_inst<THREADS, E, VAR_ABS>(a, stream);
 }
 
 // max(N, M) <= 16384

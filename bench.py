@@ -417,8 +417,8 @@ def run_ours(args, rank, world, local_rank):
     achieved_op = ab / (ms * 1e-3) / 1e9
     # dominant kernel: the emitting pass of the walk; its launch time is measured live by the stage-timing entry point
     achieved = ab / (stage["walk_pass2_ms"] * 1e-3) / 1e9
-    # DRAM traffic of one walk launch (dram__bytes_read + dram__bytes_write of an ncu capture at 12 heads, scaled
-    # by the heads of a launch: every array of the walk grows in proportion to them)
+    # DRAM traffic of one launch of the dominant kernel (from an ncu capture at 12 heads, scaled by the heads of a
+    # launch: every array the kernel touches grows in proportion to them)
     traffic = WALK_DRAM_BYTES_PER_HEAD * Ps
     sm_clock = 1e6 * (clk.get("sm_max_mhz") or 1965.0)
     line = {
@@ -440,7 +440,7 @@ def run_ours(args, rank, world, local_rank):
                      # ceilings of this formulation that sit far below the HBM one (per launch, this rank's heads):
                      # issue slots of the packed fp32 recurrences and emission ((4 N + 2 M) C / 2 per segment), and the
                      # L2 floor: two 256-byte-row gathers and one row reduction per segment at the rates a bare
-                     # gather / vector-reduction loop reaches on this GPU (17.1 and 6.1 TB/s, overlapped: 3.04 ms for 48 heads)
+                     # gather / vector-reduction loop reaches on this GPU (17.2 and 6.1 TB/s, overlapped: 3.03 ms for 48 heads)
                      "fp32_floor_ms": 1e3 * Ps * D * (4 * N + 2 * N) * C / 2 / (148 * 128 * sm_clock),
                      "l2_floor_ms": L2_FLOOR_MS_PER_HEAD * Ps},
     }
@@ -453,10 +453,11 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
-# figures from a profiler capture of the walk (DRAM bytes of one launch over 48 heads) and from a bare gather / reduction loop
-# with the walk's access pattern (two row gathers and one row reduction per segment, 48 heads), both on a B200
-WALK_DRAM_BYTES_PER_HEAD = 6.07e9 / 48
-L2_FLOOR_MS_PER_HEAD = 3.04 / 48
+# figures from a profiler capture of the dominant kernel (dram__bytes_read + dram__bytes_write of one laplace_pass2 launch over
+# 12 heads: 845.7 MB + 43.3 MB) and from a bare gather / reduction loop with the walk's access pattern (two row gathers and one
+# row reduction per segment, 48 heads: 3.03 ms), both on a B200
+WALK_DRAM_BYTES_PER_HEAD = (845.66e6 + 43.32e6) / 12
+L2_FLOOR_MS_PER_HEAD = 3.034 / 48
 
 
 def main():

@@ -90,10 +90,12 @@ int sm_count() {
 // How a walk over `nseg` segments of N keys is cut into streams, work items and CTAs. Streams are independent
 // work units (the passes exchange their states through memory), so a segment may be cut into any number of them:
 // more streams until the persistent CTAs of the second pass get about sixteen items each, as long as a stream
-// keeps at least sixteen key blocks (the staging ring needs a few blocks to fill).
+// keeps at least sixteen key blocks (the staging ring needs a few blocks to fill) - eight while there are fewer
+// items than CTAs. The prefix walks need no first pass with one stream per segment, which pays as soon as whole
+// segments alone give every CTA a few items.
 struct WalkPlan { int sps, nitems, grid1, grid2; };
 
-WalkPlan plan_walk(int nseg, int N, int C4) {
+WalkPlan plan_walk(int nseg, int N, int C4, bool laplace) {
     const int lps      = walk_lanes_per_stream(C4);
     const int streams  = walk_threads() / lps;       // streams per CTA and work item
     const int sms      = sm_count();
@@ -102,7 +104,8 @@ WalkPlan plan_walk(int nseg, int N, int C4) {
     const int nbk      = nblocks(N);
     auto items = [&](long long sps) { return (long long)(((long long)nseg * sps + streams - 1) / streams); };
     int sps = 1;
-    while (items(sps) < 16LL * cap2 && nbk / (sps * 2) >= 16 && sps < 4096) sps *= 2;
+    if (laplace || items(1) < 2LL * cap2)
+        while (items(sps) < 16LL * cap2 && nbk / (sps * 2) >= (items(sps) < cap2 ? 8 : 16) && sps < 4096) sps *= 2;
     WalkPlan w;
     w.sps    = sps;
     w.nitems = (int)items(sps);
@@ -176,7 +179,7 @@ struct LaplaceWs {
         vpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
         opad = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
         rec.carve(b, nseg, N, M);
-        plan = plan_walk(nseg, N, C4);
+        plan = plan_walk(nseg, N, C4, true);
         ckpt = b.take<float>((size_t)nseg * nblocks(N) * C4);
         wck  = b.take<float>((size_t)nseg * nblocks(N));
         agg  = b.take<float>(walk_agg_floats(plan, nseg, C4, true));
@@ -195,8 +198,8 @@ struct LaplaceBwdWs {
         gvpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
         const int mx = N > M ? N : M;
         rec.carve(b, nseg, mx, mx);
-        plan_k = plan_walk(nseg, N, C4);        // stream of keys k (grad_q)
-        plan_q = plan_walk(nseg, M, C4);        // stream of keys q (grad_v, grad_k)
+        plan_k = plan_walk(nseg, N, C4, true);  // stream of keys k (grad_q)
+        plan_q = plan_walk(nseg, M, C4, true);  // stream of keys q (grad_v, grad_k)
         const size_t slots = (size_t)nseg * nblocks(mx);
         ckpt = b.take<float>(slots * C4);
         wck  = b.take<float>(slots);
@@ -220,7 +223,7 @@ struct AbsFwdWs {
         vsum  = b.take<float>((size_t)P * C4 * 2 + P);     // vsum | ktot | ksr, zeroed together
         ktot  = vsum ? vsum + (size_t)P * C4 : nullptr;
         ksr   = vsum ? ktot + (size_t)P * C4 : nullptr;
-        plan  = plan_walk(nseg, N, C4);
+        plan  = plan_walk(nseg, N, C4, false);
         agg   = b.take<float>(walk_agg_floats(plan, nseg, C4, false));
         bytes = (b.off + 255) & ~size_t(255);
     }
@@ -243,8 +246,8 @@ struct AbsBwdWs {
         qsumd = b.take<float>((size_t)P * M);
         ksumd = b.take<float>((size_t)P * N);
         sums  = b.take<float>((size_t)P * C4 * 3 + P);
-        plan_k = plan_walk(nseg, N, C4);
-        plan_q = plan_walk(nseg, M, C4);
+        plan_k = plan_walk(nseg, N, C4, false);
+        plan_q = plan_walk(nseg, M, C4, false);
         const size_t agg_k = walk_agg_floats(plan_k, nseg, C4, false), agg_q = walk_agg_floats(plan_q, nseg, C4, false);
         agg   = b.take<float>(agg_k > agg_q ? agg_k : agg_q);
         bytes = (b.off + 255) & ~size_t(255);

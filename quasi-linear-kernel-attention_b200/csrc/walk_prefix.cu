@@ -5,7 +5,9 @@
 //              with e0 = 2 * query and e1 = -2 this is the walk term 2 (q PV - PK) of the abs sum; folded
 //              queries (shifted, weighted copies that share a row) scale both by their weight
 //              (Weighted_Abs_Sum/csrc/abs_kernels.cu:9-18; abs_chunk :78-199, abs_prefix :202-405)
-//   EMIT_BOTH  both of the others from one walk (grad_v and grad_k share stream, rows and queries)
+//   EMIT_BOTH  both of the others over the same stream, rows and queries (grad_v and grad_k): one first pass and fold,
+//              then the row emission and the dot emission as two second passes (one kernel doing both needs more than
+//              the 128 registers that two resident CTAs leave a thread, and its spills cost more than the second walk)
 //   EMIT_DOT   out_s[seg, row_m] = sign * ( <g[p, row_m, :], 2 PV - wtotal[p, :]> + e1_m )
 //              the signed-rank walk behind grad_q, grad_k and the public sgn op
 //              (Weighted_Abs_Sum/csrc/sgn_kernels.cu:8-15, sgn_prefix :17-192); one writer per
@@ -20,7 +22,8 @@
 
 namespace qlka {
 
-enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2 };     // BOTH: one walk feeds a row reduction and a dot output
+enum { EMIT_ROWS = 0, EMIT_DOT = 1, EMIT_BOTH = 2,       // BOTH (host level): row reductions and dots over the same stream and queries
+       EMIT_ROWS_FIXED = 3 };                           // its row part: the key-sum coefficient is the constant -2, the record's e1 belongs to the dot
 
 // floats per stream in the aggregate table: sum of the stream's rows | sum of key * row
 __host__ __device__ inline int prefix_agg_stride(int C4) { return 2 * C4; }
@@ -137,7 +140,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
 {
     constexpr int  STREAMS = WALK_THREADS / LPS;
     constexpr bool WITH_K  = EMIT != EMIT_DOT;
-    constexpr bool DO_ROWS = EMIT != EMIT_DOT, DO_DOT = EMIT != EMIT_ROWS;
+    constexpr bool DO_ROWS = EMIT != EMIT_DOT, DO_DOT = EMIT == EMIT_DOT;
     extern __shared__ __align__(16) float4 smem[];
     float4* ring   = smem;
     uint4*  qs_all = reinterpret_cast<uint4*>(reinterpret_cast<char*>(ring) + ring_bytes<CPL>());
@@ -263,7 +266,7 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
                 auto emit_rows = [&](const uint4 rec, const Vec<CPL>& Pq, const Vec<CPL>& Kq) {
                     if (DO_ROWS) {
                         const float e0 = __uint_as_float(rec.x);
-                        const float ek = EMIT == EMIT_ROWS ? __uint_as_float(rec.y) : -2.0f;     // (rec.y is the dot term's addend in EMIT_BOTH)
+                        const float ek = EMIT == EMIT_ROWS ? __uint_as_float(rec.y) : -2.0f;     // (rec.y is the dot term's addend otherwise)
                         if (on) {
                             float* o = out + (size_t)rec.z * C4;
                             #pragma unroll
@@ -356,41 +359,48 @@ __global__ void __launch_bounds__(WALK_THREADS, (CPL <= 4 ? WALK_MIN_CTAS : 1)) 
 }
 
 template <int LPS, int CPL, int EMIT>
-static cudaError_t launch_pw(const WalkArgs& a, int grid1, int grid2, cudaStream_t stream) {
-    constexpr bool WITH_K = EMIT != EMIT_DOT;
-    auto k1 = prefix_pass1<LPS, CPL, WITH_K>;
+static cudaError_t launch_pass2(const WalkArgs& a, int grid2, cudaStream_t stream) {
     auto k2 = prefix_pass2<LPS, CPL, EMIT>;
-    const size_t smem1 = pass1_smem_bytes<LPS, CPL>();
-    const size_t smem2 = walk_smem_bytes<LPS, CPL>() + (EMIT != EMIT_ROWS ? g_area_bytes<CPL>() : 0);
-    cudaError_t e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+    const size_t smem2 = walk_smem_bytes<LPS, CPL>() + (EMIT == EMIT_DOT ? g_area_bytes<CPL>() : 0);
+    cudaError_t e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);
-    if (e != cudaSuccess) return e;
-    if (a.sps > 1) {                                                   // (a lone stream per segment has nothing before it)
-        k1<<<grid1, WALK_THREADS, smem1, stream>>>(a);
-        prefix_fold<<<(unsigned)(((long long)a.nseg * a.C4 + 255) / 256), 256, 0, stream>>>(a.agg, a.nseg, a.sps, a.C4, WITH_K ? 1 : 0);
-    }
     k2<<<grid2, WALK_THREADS, smem2, stream>>>(a);
     return cudaGetLastError();
 }
 
+template <int LPS, int CPL>
+static cudaError_t launch_pw(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream) {
+    if (a.sps > 1) {                                                   // (a lone stream per segment has nothing before it)
+        const size_t smem1 = pass1_smem_bytes<LPS, CPL>();
+        cudaError_t e;
+        if (emit == EMIT_DOT) {
+            auto k1 = prefix_pass1<LPS, CPL, false>;
+            e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+            if (e != cudaSuccess) return e;
+            k1<<<grid1, WALK_THREADS, smem1, stream>>>(a);
+        } else {
+            auto k1 = prefix_pass1<LPS, CPL, true>;
+            e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1);
+            if (e != cudaSuccess) return e;
+            k1<<<grid1, WALK_THREADS, smem1, stream>>>(a);
+        }
+        prefix_fold<<<(unsigned)(((long long)a.nseg * a.C4 + 255) / 256), 256, 0, stream>>>(a.agg, a.nseg, a.sps, a.C4, emit == EMIT_DOT ? 0 : 1);
+    }
+    if (emit == EMIT_ROWS) return launch_pass2<LPS, CPL, EMIT_ROWS>(a, grid2, stream);
+    if (emit == EMIT_DOT)  return launch_pass2<LPS, CPL, EMIT_DOT>(a, grid2, stream);
+    cudaError_t e = launch_pass2<LPS, CPL, EMIT_ROWS_FIXED>(a, grid2, stream);       // EMIT_BOTH
+    if (e != cudaSuccess) return e;
+    return launch_pass2<LPS, CPL, EMIT_DOT>(a, grid2, stream);
+}
+
 int prefix_agg_stride_host(int C4) { return prefix_agg_stride(C4); }
 
-// grid1 / grid2: CTAs of the two launches
+// emit: EMIT_ROWS, EMIT_DOT or EMIT_BOTH; grid1 / grid2: CTAs of the first and of the emitting launches
 cudaError_t launch_prefix_walk(const WalkArgs& a, int emit, int grid1, int grid2, cudaStream_t stream) {
-    if (emit == EMIT_ROWS) {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_ROWS>(a, grid1, grid2, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_ROWS>(a, grid1, grid2, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_ROWS>(a, grid1, grid2, stream);
-    } else if (emit == EMIT_DOT) {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_DOT>(a, grid1, grid2, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_DOT>(a, grid1, grid2, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_DOT>(a, grid1, grid2, stream);
-    } else {
-        if (a.C4 <= 32)  return launch_pw<8, 4, EMIT_BOTH>(a, grid1, grid2, stream);
-        if (a.C4 <= 64)  return launch_pw<16, 4, EMIT_BOTH>(a, grid1, grid2, stream);
-        if (a.C4 <= 128) return launch_pw<16, 8, EMIT_BOTH>(a, grid1, grid2, stream);
-    }
+    if (emit != EMIT_ROWS && emit != EMIT_DOT && emit != EMIT_BOTH) return cudaErrorInvalidValue;
+    if (a.C4 <= 32)  return launch_pw<8, 4>(a, emit, grid1, grid2, stream);
+    if (a.C4 <= 64)  return launch_pw<16, 4>(a, emit, grid1, grid2, stream);
+    if (a.C4 <= 128) return launch_pw<16, 8>(a, emit, grid1, grid2, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -196,47 +196,48 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
     // x_j = A_j x_{j-1} + B_j over the segment, forward (into su0) and, for the Laplace unit column,
     // backward (into su1); a tile at a time with the state carried in shared memory
     const float* us  = (a.scal == SCAL_PREFIX || (a.scal == SCAL_SIGNED && a.us)) ? a.us + (long long)p * N : nullptr;
+    // Every warp owns 32 * LE consecutive scan positions of the tile, lane l the positions k * 32 + l (so that each load
+    // and store of a warp is one contiguous line); a row of 32 is scanned with shuffles, rows are chained through the
+    // composite of the rows before, warps through shared memory, tiles through `carry`.
     for (int dir = 0; dir < (lap ? 2 : 1); dir++) {
         if (tid == 0) carry[0] = 0.0f;
         __syncthreads();
+        float* dst = dir ? su1 : su0;
         for (long long t0 = 0; t0 < N; t0 += LTILE) {
             // scan position i (0-based in scan order) <-> key j = i (forward) or N-1-i (backward)
-            float A[LE], B[LE];
-            float ca = 1.0f, cb = 0.0f;
+            float ta[LE], tb[LE];                     // state at position (k, lane) = ta * (state entering the warp's chunk) + tb
+            float ca = 1.0f, cb = 0.0f;               // the same for the end of the previous row
+            const long long base = t0 + (long long)warp * 32 * LE;
             #pragma unroll
             for (int k = 0; k < LE; k++) {
-                const long long i = t0 + (long long)tid * LE + k;
-                const int       j = dir ? N - 1 - (int)i : (int)i;
+                const long long i = base + k * 32 + lane;
+                float ia = 1.0f, ib = 0.0f;
                 if (i < N) {
-                    A[k] = lap ? (dir ? dec_at(j + 1) : dec_at(j)) : 1.0f;
-                    B[k] = us ? us[isorted[j]] : (lap ? 1.0f : xs[j]);
-                } else { A[k] = 1.0f; B[k] = 0.0f; }
-                ca = A[k] * ca; cb = fmaf(A[k], cb, B[k]);
-            }
-            float ia = ca, ib = cb;
-            #pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                float pa = __shfl_up_sync(FULL, ia, off), pb = __shfl_up_sync(FULL, ib, off);
-                if (lane >= off) { ib = fmaf(ia, pb, ib); ia = ia * pa; }
-            }
-            if (lane == 31) { wa[warp] = ia; wb[warp] = ib; }
-            __syncthreads();
-            float pb = carry[0];
-            for (int w = 0; w < warp; w++) pb = fmaf(wa[w], pb, wb[w]);
-            float ea = __shfl_up_sync(FULL, ia, 1), eb = __shfl_up_sync(FULL, ib, 1);
-            if (lane == 0) { ea = 1.0f; eb = 0.0f; }
-            float x = fmaf(ea, pb, eb);
-            #pragma unroll
-            for (int k = 0; k < LE; k++) {
-                const long long i = t0 + (long long)tid * LE + k;
-                if (i < N) {
-                    x = fmaf(A[k], x, B[k]);
                     const int j = dir ? N - 1 - (int)i : (int)i;
-                    (dir ? su1 : su0)[j] = x;
+                    ia = lap ? (dir ? dec_at(j + 1) : dec_at(j)) : 1.0f;
+                    ib = us ? us[isorted[j]] : (lap ? 1.0f : xs[j]);
                 }
+                #pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const float pa = __shfl_up_sync(FULL, ia, off), pb = __shfl_up_sync(FULL, ib, off);
+                    if (lane >= off) { ib = fmaf(ia, pb, ib); ia = ia * pa; }
+                }
+                ta[k] = ia * ca;
+                tb[k] = fmaf(ia, cb, ib);
+                ca = __shfl_sync(FULL, ta[k], 31);
+                cb = __shfl_sync(FULL, tb[k], 31);
+            }
+            if (lane == 0) { wa[warp] = ca; wb[warp] = cb; }
+            __syncthreads();
+            float x0 = carry[0];                       // state entering this warp's chunk
+            for (int w = 0; w < warp; w++) x0 = fmaf(wa[w], x0, wb[w]);
+            #pragma unroll
+            for (int k = 0; k < LE; k++) {
+                const long long i = base + k * 32 + lane;
+                if (i < N) dst[dir ? N - 1 - (int)i : (int)i] = fmaf(ta[k], x0, tb[k]);
             }
             __syncthreads();
-            if (tid == LT - 1) carry[0] = x;          // state after the tile's last position (padding positions are identity)
+            if (tid == LT - 32) carry[0] = fmaf(ca, x0, cb);      // (lane 0 of the last warp) state after the tile; padding positions are identity
             __syncthreads();
         }
     }

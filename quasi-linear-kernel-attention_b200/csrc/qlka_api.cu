@@ -170,26 +170,78 @@ bool ws_ok(const void* ws, size_t have, size_t need) {
     return need == 0 || (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && have >= need);
 }
 
+// ------------------------------------------------------------------ Laplace walk, a few heads at a time
+// The first walk pass leaves one suffix checkpoint per block of 8 keys and segment for the second pass: D / 8 times the
+// size of the row matrix. So that this scratch does not grow with the batch, the walk runs over chunks of whole heads whose
+// checkpoints stay under CKPT_BUDGET (one chunk for everything up to B=4,H=12,N=16384,D=C=64 and beyond).
+constexpr size_t CKPT_BUDGET = size_t(2) << 30;
+
+int laplace_chunk_heads(int P, int D, int N, int C4) {
+    const size_t per_head = (size_t)D * nblocks(N) * C4 * sizeof(float);
+    size_t h = CKPT_BUDGET / per_head;
+    if (h < 1) h = 1;
+    return (int)(h < (size_t)P ? h : (size_t)P);
+}
+
+struct LapWalkScratch {
+    float *ckpt, *wck, *agg; int heads;
+    void carve(Bump& b, int P, int D, int N, int C4) {
+        heads = laplace_chunk_heads(P, D, N, C4);
+        const int nseg_c = heads * D;
+        ckpt = b.take<float>((size_t)nseg_c * nblocks(N) * C4);
+        wck  = b.take<float>((size_t)nseg_c * nblocks(N));
+        // the aggregate table of the larger of the two chunk sizes that occur (full chunks and the remainder)
+        size_t a = walk_agg_floats(plan_walk(nseg_c, N, C4, true), nseg_c, C4, true);
+        if (const int rem = P % heads) {
+            const size_t a2 = walk_agg_floats(plan_walk(rem * D, N, C4, true), rem * D, C4, true);
+            if (a2 > a) a = a2;
+        }
+        agg = b.take<float>(a);
+    }
+};
+
+// rows (P, N, C4): the stream's rows; out (P, Mrows, C4) / g (P, M, C4) / out_s (P*D, M) as the emission needs them;
+// mid: optional event between the passes of the first chunk (the stage timing of a single-chunk call)
+cudaError_t laplace_walk_chunked(const Records& r, const LapWalkScratch& sc, const float* rows, float* out, const float* g, float* out_s,
+                                 int emit, int P, int D, int N, int M, int C4, cudaStream_t stream, cudaEvent_t mid)
+{
+    for (int p0 = 0; p0 < P; p0 += sc.heads) {
+        const int       pc = sc.heads < P - p0 ? sc.heads : P - p0, nseg = pc * D;
+        const long long s0 = (long long)p0 * D;
+        const WalkPlan  plan = plan_walk(nseg, N, C4, true);
+        WalkArgs a{};
+        a.rows = rows + (size_t)p0 * N * C4;
+        a.xperm = r.xperm + s0 * npad(N); a.xval = r.xval + s0 * xstride(N);
+        a.yrec = r.yrec + s0 * (M + 1);   a.mstart = r.mstart + s0 * mstride(N);
+        a.ckpt = sc.ckpt; a.wck = sc.wck; a.agg = sc.agg;
+        a.out   = out ? out + (size_t)p0 * M * C4 : nullptr;
+        a.g     = g ? g + (size_t)p0 * M * C4 : nullptr;
+        a.out_s = out_s ? out_s + s0 * M : nullptr;
+        a.nseg = nseg; a.D = D; a.N = N; a.M = M; a.C4 = C4; a.sps = plan.sps; a.nitems = plan.nitems;
+        a.sign = 1.0f; a.Mrows = M;
+        cudaError_t e = launch_laplace_walk(a, emit, plan.grid1, plan.grid2, stream, p0 == 0 ? mid : nullptr);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
 // ------------------------------------------------------------------ Laplace forward
 struct LaplaceWs {
-    float* vpad; float* opad; Records rec; float* ckpt; float* wck; float* agg; WalkPlan plan; size_t bytes;
+    float* vpad; float* opad; Records rec; LapWalkScratch walk; size_t bytes;
     LaplaceWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
         vpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
         opad = C4 != C ? b.take<float>((size_t)P * M * C4) : nullptr;
         rec.carve(b, nseg, N, M);
-        plan = plan_walk(nseg, N, C4, true);
-        ckpt = b.take<float>((size_t)nseg * nblocks(N) * C4);
-        wck  = b.take<float>((size_t)nseg * nblocks(N));
-        agg  = b.take<float>(walk_agg_floats(plan, nseg, C4, true));
+        walk.carve(b, P, D, N, C4);
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
 
 // ------------------------------------------------------------------ Laplace backward
 struct LaplaceBwdWs {
-    float *vpad, *gpad, *gvpad; Records rec; float* ckpt; float* wck; float* agg; WalkPlan plan_k, plan_q; size_t bytes;
+    float *vpad, *gpad, *gvpad; Records rec; LapWalkScratch walk; size_t bytes;
     LaplaceBwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
@@ -198,13 +250,7 @@ struct LaplaceBwdWs {
         gvpad = C4 != C ? b.take<float>((size_t)P * N * C4) : nullptr;
         const int mx = N > M ? N : M;
         rec.carve(b, nseg, mx, mx);
-        plan_k = plan_walk(nseg, N, C4, true);  // stream of keys k (grad_q)
-        plan_q = plan_walk(nseg, M, C4, true);  // stream of keys q (grad_v, grad_k)
-        const size_t slots = (size_t)nseg * nblocks(mx);
-        ckpt = b.take<float>(slots * C4);
-        wck  = b.take<float>(slots);
-        const size_t agg_k = walk_agg_floats(plan_k, nseg, C4, true), agg_q = walk_agg_floats(plan_q, nseg, C4, true);
-        agg  = b.take<float>(agg_k > agg_q ? agg_k : agg_q);
+        walk.carve(b, P, D, mx, C4);            // one scratch for both walks (stream of keys k, then stream of keys q): sized for the longer
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
@@ -315,9 +361,7 @@ static int laplace_forward_impl(const float* q, const float* k, const float* v,
     CU(launch_sort_rank(s, ws.rec, stream));
     if (ev) CU(cudaEventRecord(ev[1], stream));
 
-    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, M, C4);
-    w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.out = out;
-    CU(launch_laplace_walk(w, EMIT_ROWS, ws.plan.grid1, ws.plan.grid2, stream, ev ? ev[2] : nullptr));
+    CU(laplace_walk_chunked(ws.rec, ws.walk, rows, out, nullptr, nullptr, EMIT_ROWS, P, D, N, M, C4, stream, ev ? ev[2] : nullptr));
     if (ev) CU(cudaEventRecord(ev[3], stream));
 
     if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
@@ -395,18 +439,14 @@ int qlka_weighted_laplace_sum_backward(const float* q, const float* k, const flo
         SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_LAPLACE, full ? SCAL_SIGNED : SCAL_NONE);
         s.uq = g_u; s.out_s = grad_q;
         CU(launch_sort_rank(s, ws.rec, stream));
-        WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
-        w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.g = grows; w.out_s = grad_q;
-        CU(launch_laplace_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream, nullptr));
+        CU(laplace_walk_chunked(ws.rec, ws.walk, vrows, nullptr, grows, grad_q, EMIT_DOT, P, D, N, M, C4, stream, nullptr));
     }
     {   // roles swapped: queries k walk the stream q whose rows are g_w (and whose per-key scalar is g_u);
         // the row emission is grad_v, the dot with the v rows is grad_k
         SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_LAPLACE, full ? SCAL_SIGNED : SCAL_NONE);
         s.us = g_u; s.out_s = grad_k;
         CU(launch_sort_rank(s, ws.rec, stream));
-        WalkArgs w = walk_args(ws.rec, ws.plan_q, grows, nseg, D, M, N, C4);
-        w.ckpt = ws.ckpt; w.wck = ws.wck; w.agg = ws.agg; w.g = vrows; w.out_s = grad_k; w.out = gv;
-        CU(launch_laplace_walk(w, EMIT_BOTH, ws.plan_q.grid1, ws.plan_q.grid2, stream, nullptr));
+        CU(laplace_walk_chunked(ws.rec, ws.walk, grows, gv, vrows, grad_k, EMIT_BOTH, P, D, M, N, C4, stream, nullptr));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
     return QLKA_OK;

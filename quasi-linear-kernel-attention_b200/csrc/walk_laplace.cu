@@ -443,8 +443,6 @@ int walk_lanes_per_stream(int C4) { return C4 <= 32 ? 8 : 16; }
 int walk_threads() { return WALK_THREADS; }
 
 int laplace_agg_stride(int C4) { return lap_agg_stride(C4); }
-// resident CTAs per SM of the two passes (what the host sizes their grids with)
-int laplace_pass_ctas_per_sm(int C4, int pass) { return C4 <= 64 ? (pass == 1 ? 3 : WALK_MIN_CTAS) : 1; }
 
 // emit: 0 = row reductions (the forward sum), 1 = dot, 2 = both; grid1 / grid2: CTAs of the two passes;
 // mid: optional event recorded between the first pass (with the fold) and the second

@@ -148,10 +148,10 @@ cudaError_t launch_sort_rank(const SortArgs& s, const Records& r, cudaStream_t s
     return launch_sort_rank_large(s, r.large, stream);
 }
 
-WalkArgs walk_args(const Records& r, const WalkPlan& w, const float* rows, int nseg, int D, int N, int M, int C4) {
+WalkArgs walk_args(const Records& r, const float* rows, int nseg, int D, int N, int M, int C4) {
     WalkArgs a{};
     a.rows = rows; a.xperm = r.xperm; a.xval = r.xval; a.yrec = r.yrec; a.mstart = r.mstart;
-    a.nseg = nseg; a.D = D; a.N = N; a.M = M; a.C4 = C4; a.sps = w.sps; a.nitems = w.nitems;
+    a.nseg = nseg; a.D = D; a.N = N; a.M = M; a.C4 = C4;
     a.sign = 1.0f;
     a.Mrows = M;
     return a;
@@ -170,17 +170,66 @@ bool ws_ok(const void* ws, size_t have, size_t need) {
     return need == 0 || (ws != nullptr && (reinterpret_cast<uintptr_t>(ws) & 255) == 0 && have >= need);
 }
 
-// ------------------------------------------------------------------ Laplace walk, a few heads at a time
+// ------------------------------------------------------------------ walks, a few heads at a time
+// A walk gathers the rows of a head in 64 different orders and adds into its output rows; once the heads in flight no
+// longer fit the L2 (long sequences) it pays to finish a few heads before starting the next ones, so every walk runs over
+// chunks of whole heads whose row matrix stays under ROWS_BUDGET (one chunk up to B=4,H=12,N=16384,C=64 and well beyond;
+// 15 heads at N=65536, 3 at N=262144 with 64 channels).
+constexpr size_t ROWS_BUDGET = size_t(256) << 20;
+
+int walk_chunk_heads(int P, int N, int C4) {
+    size_t h = ROWS_BUDGET / ((size_t)N * C4 * sizeof(float));
+    if (h < 1) h = 1;
+    return (int)(h < (size_t)P ? h : (size_t)P);
+}
+
+// aggregate table of a prefix walk over P heads in chunks (the larger of the two chunk sizes that occur)
+size_t prefix_agg_floats(int P, int D, int N, int C4) {
+    const int heads = walk_chunk_heads(P, N, C4);
+    size_t a = walk_agg_floats(plan_walk(heads * D, N, C4, false), heads * D, C4, false);
+    if (const int rem = P % heads) {
+        const size_t a2 = walk_agg_floats(plan_walk(rem * D, N, C4, false), rem * D, C4, false);
+        if (a2 > a) a = a2;
+    }
+    return a;
+}
+
+// `w` describes the whole problem (pointers of head 0, nseg = P * D); every chunk gets its own plan
+cudaError_t prefix_walk_chunked(WalkArgs w, int emit, int P, cudaStream_t stream)
+{
+    const int heads = walk_chunk_heads(P, w.N, w.C4);
+    const WalkArgs all = w;
+    for (int p0 = 0; p0 < P; p0 += heads) {
+        const int       pc = heads < P - p0 ? heads : P - p0;
+        const long long s0 = (long long)p0 * all.D;
+        const WalkPlan  plan = plan_walk(pc * all.D, all.N, all.C4, false);
+        w.rows   = all.rows + (size_t)p0 * all.N * all.C4;
+        w.xperm  = all.xperm + s0 * npad(all.N);
+        w.xval   = all.xval + s0 * xstride(all.N);
+        w.yrec   = all.yrec + s0 * (all.M + 1);
+        w.mstart = all.mstart + s0 * mstride(all.N);
+        w.out    = all.out ? all.out + (size_t)p0 * all.Mrows * all.C4 : nullptr;
+        w.g      = all.g ? all.g + (size_t)p0 * all.M * all.C4 : nullptr;
+        w.wtotal = all.wtotal ? all.wtotal + (size_t)p0 * all.C4 : nullptr;
+        w.out_s  = all.out_s ? all.out_s + s0 * all.M : nullptr;
+        w.nseg = pc * all.D; w.sps = plan.sps; w.nitems = plan.nitems;
+        cudaError_t e = launch_prefix_walk(w, emit, plan.grid1, plan.grid2, stream);
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+}
+
 // The first walk pass leaves one suffix checkpoint per block of 8 keys and segment for the second pass: D / 8 times the
-// size of the row matrix. So that this scratch does not grow with the batch, the walk runs over chunks of whole heads whose
-// checkpoints stay under CKPT_BUDGET (one chunk for everything up to B=4,H=12,N=16384,D=C=64 and beyond).
+// size of the row matrix. So that this scratch does not grow with the batch, a chunk's checkpoints also stay under
+// CKPT_BUDGET (the same chunks as the rows rule at D = 64).
 constexpr size_t CKPT_BUDGET = size_t(2) << 30;
 
 int laplace_chunk_heads(int P, int D, int N, int C4) {
     const size_t per_head = (size_t)D * nblocks(N) * C4 * sizeof(float);
     size_t h = CKPT_BUDGET / per_head;
     if (h < 1) h = 1;
-    return (int)(h < (size_t)P ? h : (size_t)P);
+    const int by_rows = walk_chunk_heads(P, N, C4);
+    return (int)(h < (size_t)by_rows ? h : (size_t)by_rows);
 }
 
 struct LapWalkScratch {
@@ -257,7 +306,7 @@ struct LaplaceBwdWs {
 
 // ------------------------------------------------------------------ abs forward
 struct AbsFwdWs {
-    float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr, *agg; WalkPlan plan; size_t bytes;
+    float* vpad; float* opad; Records rec; float *qsum, *ksumd, *vsum, *ktot, *ksr, *agg; size_t bytes;
     AbsFwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
         const int C4 = round4(C), nseg = P * D;
@@ -269,8 +318,7 @@ struct AbsFwdWs {
         vsum  = b.take<float>((size_t)P * C4 * 2 + P);     // vsum | ktot | ksr, zeroed together
         ktot  = vsum ? vsum + (size_t)P * C4 : nullptr;
         ksr   = vsum ? ktot + (size_t)P * C4 : nullptr;
-        plan  = plan_walk(nseg, N, C4, false);
-        agg   = b.take<float>(walk_agg_floats(plan, nseg, C4, false));
+        agg   = b.take<float>(prefix_agg_floats(P, D, N, C4));
         bytes = (b.off + 255) & ~size_t(255);
     }
 };
@@ -279,7 +327,6 @@ struct AbsFwdWs {
 struct AbsBwdWs {
     float *vpad, *gpad, *gvpad; Records rec;
     float *qsumd, *ksumd, *sums /* vsum | gwsum | qtotg | gu_total */, *agg;
-    WalkPlan plan_k, plan_q;     // stream of keys k (grad_q, sgn) / stream of keys q (grad_v, grad_k)
     size_t bytes;
     AbsBwdWs(void* base, int P, int D, int N, int M, int C) {
         Bump b(base);
@@ -292,9 +339,7 @@ struct AbsBwdWs {
         qsumd = b.take<float>((size_t)P * M);
         ksumd = b.take<float>((size_t)P * N);
         sums  = b.take<float>((size_t)P * C4 * 3 + P);
-        plan_k = plan_walk(nseg, N, C4, false);
-        plan_q = plan_walk(nseg, M, C4, false);
-        const size_t agg_k = walk_agg_floats(plan_k, nseg, C4, false), agg_q = walk_agg_floats(plan_q, nseg, C4, false);
+        const size_t agg_k = prefix_agg_floats(P, D, N, C4), agg_q = prefix_agg_floats(P, D, M, C4);
         agg   = b.take<float>(agg_k > agg_q ? agg_k : agg_q);
         bytes = (b.off + 255) & ~size_t(255);
     }
@@ -684,9 +729,9 @@ static int abs_forward_impl(const float* q, const float* k, const float* v, floa
     if (ns) { s.fold = M; for (int i = 0; i < ns; i++) { s.shift[i] = shifts[i]; s.wgt[i] = weights[i]; } }
     CU(launch_sort_rank(s, ws.rec, stream));
 
-    WalkArgs w = walk_args(ws.rec, ws.plan, rows, nseg, D, N, MQ, C4);
+    WalkArgs w = walk_args(ws.rec, rows, nseg, D, N, MQ, C4);
     w.out = out; w.Mrows = M; w.agg = ws.agg;
-    CU(launch_prefix_walk(w, EMIT_ROWS, ws.plan.grid1, ws.plan.grid2, stream));
+    CU(prefix_walk_chunked(w, EMIT_ROWS, P, stream));
 
     if (C4 != C) CU(launch_unpad_rows(out, out_w, (long long)P * M, C, C4, stream));
     return QLKA_OK;
@@ -779,9 +824,9 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
         SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, full ? SCAL_RANK : SCAL_NONE);
         s.uq = g_u;
         CU(launch_sort_rank(s, ws.rec, stream));
-        WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
+        WalkArgs w = walk_args(ws.rec, vrows, nseg, D, N, M, C4);
         w.g = grows; w.wtotal = vsum; w.out_s = grad_q; w.agg = ws.agg;
-        CU(launch_prefix_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream));
+        CU(prefix_walk_chunked(w, EMIT_DOT, P, stream));
     }
     {   // roles swapped: queries k walk the stream q whose rows are g_w
         SortArgs s = sort_args(ws.rec, q, k, nseg, D, M, N, MODE_ABS, full ? SCAL_PREFIX : SCAL_NONE);
@@ -790,9 +835,9 @@ int qlka_weighted_abs_sum_backward(const float* q, const float* k, const float* 
         // one walk for both: grad_v = abs sum with keys q, weights g_w, evaluated at the keys k (row reductions on
         // top of its rank-1 initial value); grad_k = prefix of g_w rows contracted with v rows (+ the g_u term in e1)
         CU(launch_abs_init(qtotg, gwsum, ws.ksumd, nullptr, gv, nullptr, P, N, C4, M, 1.0f, 0.0f, stream));
-        WalkArgs w = walk_args(ws.rec, ws.plan_q, grows, nseg, D, M, N, C4);
+        WalkArgs w = walk_args(ws.rec, grows, nseg, D, M, N, C4);
         w.g = vrows; w.wtotal = gwsum; w.out_s = grad_k; w.out = gv; w.agg = ws.agg;
-        CU(launch_prefix_walk(w, EMIT_BOTH, ws.plan_q.grid1, ws.plan_q.grid2, stream));
+        CU(prefix_walk_chunked(w, EMIT_BOTH, P, stream));
     }
     if (C4 != C) CU(launch_unpad_rows(gv, grad_v, (long long)P * N, C, C4, stream));
     return QLKA_OK;
@@ -829,9 +874,9 @@ int qlka_weighted_sgn_sum_forward(const float* q, const float* k, const float* v
 
     SortArgs s = sort_args(ws.rec, k, q, nseg, D, N, M, MODE_SGN, SCAL_NONE);
     CU(launch_sort_rank(s, ws.rec, stream));
-    WalkArgs w = walk_args(ws.rec, ws.plan_k, vrows, nseg, D, N, M, C4);
+    WalkArgs w = walk_args(ws.rec, vrows, nseg, D, N, M, C4);
     w.g = grows; w.wtotal = vsum; w.out_s = out; w.sign = -1.0f; w.agg = ws.agg;
-    CU(launch_prefix_walk(w, EMIT_DOT, ws.plan_k.grid1, ws.plan_k.grid2, stream));
+    CU(prefix_walk_chunked(w, EMIT_DOT, P, stream));
     return QLKA_OK;
 }
 

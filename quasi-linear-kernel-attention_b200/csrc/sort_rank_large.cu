@@ -146,11 +146,12 @@ __host__ __device__ inline int       large_nb(int n)      { return n / 4 + 1; }
 __host__ __device__ inline long long large_bstride(int n) { return (long long)large_nb(n) + 3; }
 struct BucketMap {
     float lo, scale; int nb;
-    __device__ __forceinline__ BucketMap(const float* __restrict__ xs, const int n) {
-        lo = __ldg(xs); nb = large_nb(n);
-        const float width = __ldg(xs + n - 1) - lo;
+    __device__ __forceinline__ BucketMap(const float smallest, const float largest, const int n) {
+        lo = smallest; nb = large_nb(n);
+        const float width = largest - smallest;
         scale = (width > 1e-30f && width < 1e30f) ? (float)nb / width : 0.0f;
     }
+    __device__ __forceinline__ BucketMap(const float* __restrict__ xs, const int n) : BucketMap(__ldg(xs), __ldg(xs + n - 1), n) {}
     __device__ __forceinline__ int operator()(const float v) const { return (int)fminf(fmaxf((v - lo) * scale, 0.0f), (float)(nb - 1)); }
 };
 
@@ -170,25 +171,26 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
     float*    su0   = a.su0 + seg * (N + 1);
     float*    su1   = a.su1 + seg * (N + 1);
 
-    for (int j = tid; j < NP + KB; j += LT) {
-        if (j < N) xs[j] = key2f(ksorted[j]);
-        if (j < NP) xperm[j] = j < N ? isorted[j] : 0u;
-    }
-    __syncthreads();
+    // one sweep over the sorted keys: key values, permutation, per-key scalar (decay or key) and the bucket index, each key read
+    // once together with its predecessor
+    const bool lap = a.mode == MODE_LAPLACE;
     {
-        const BucketMap bucket(xs, N);
+        const BucketMap bucket(key2f(ksorted[0]), key2f(ksorted[N - 1]), N);
         uint32_t* bst = bst_all + seg * large_bstride(N);
-        for (int j = tid; j < N; j += LT) {
-            const int b = bucket(xs[j]), prev = j > 0 ? bucket(xs[j - 1]) : -1;
-            for (int t = prev + 1; t <= b; t++) bst[t] = (uint32_t)j;
-            if (j == N - 1) for (int t = b + 1; t <= bucket.nb; t++) bst[t] = (uint32_t)N;
+        for (int j = tid; j < NP + KB; j += LT) {
+            if (j < N) {
+                const float x = key2f(ksorted[j]), xp = j > 0 ? key2f(ksorted[j - 1]) : 0.0f;
+                xs[j] = x;
+                const int b = bucket(x), prev = j > 0 ? bucket(xp) : -1;
+                for (int t = prev + 1; t <= b; t++) bst[t] = (uint32_t)j;
+                if (j == N - 1) for (int t = b + 1; t <= bucket.nb; t++) bst[t] = (uint32_t)N;
+                if (a.mode != MODE_SGN) xval[j] = lap ? (j > 0 ? decay_of(x - xp) : 0.0f) : x;
+            } else if (a.mode != MODE_SGN) {
+                xval[j] = lap ? 1.0f : 0.0f;
+            }
+            if (j < NP) xperm[j] = j < N ? isorted[j] : 0u;
         }
     }
-    const bool lap = a.mode == MODE_LAPLACE;
-    auto dec = [&](int j) -> float { return (j > 0 && j < N) ? decay_of(xs[j] - xs[j - 1]) : 0.0f; };
-    if (a.mode != MODE_SGN)
-        for (int j = tid; j < NP + KB; j += LT)
-            xval[j] = lap ? (j < N ? dec(j) : 1.0f) : (j < N ? xs[j] : 0.0f);
     if (a.scal != SCAL_UNIT && a.scal != SCAL_PREFIX && a.scal != SCAL_SIGNED) return;
     __syncthreads();          // the scans read the decays back from xval instead of taking every exponential three times
     auto dec_at = [&](int j) -> float { return (j > 0 && j < N) ? xval[j] : 0.0f; };

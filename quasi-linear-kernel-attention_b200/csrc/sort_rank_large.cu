@@ -3,9 +3,9 @@
 // memory (L2 resident per CTA) and stream it through shared memory a tile at a time.
 //
 //   seg_radix_pass   one CTA per segment, one launch per 8-bit digit: digit histogram of the whole
-//                    segment, then tile by tile (16384 elements) the stable in-tile ranking of the
-//                    shared-memory sort, a tile-local reorder in shared memory, and run-wise coalesced
-//                    writes to the segment's output buffer at the running digit offsets.
+//                    segment (all four counted by the first launch), then tile by tile (8192 elements) the
+//                    stable in-tile ranking of the shared-memory sort, a tile-local reorder in shared memory,
+//                    and run-wise coalesced writes to the segment's output buffer at the running digit offsets.
 //   key_scalars      per segment: sorted key values, permutation, per-key decays / key values, the
 //                    scalar scans (unit column or prefix of a per-key scalar), tile by tile with a
 //                    carried state, and a bucket index over the sorted keys for the rank search.
@@ -30,37 +30,65 @@ constexpr int LW = LT / 32;
 
 __host__ __device__ inline long long large_pad(int n) { return ((long long)n + LTILE - 1) / LTILE * LTILE; }
 
-// One 8-bit pass over every segment. pass 0 reads the float source (and creates the index payload),
-// later passes read the previous pass's buffers.
-__global__ void __launch_bounds__(LT, 1) seg_radix_pass(
+// One 8-bit pass over every segment: one CTA per segment, two CTAs per SM (so that one ranks a tile while
+// the other waits for its loads), tiles of RT * RE elements. The first pass reads the float source, creates
+// the index payload and counts the digits of all four passes in one sweep (the digit histogram of a whole
+// segment does not depend on the order of its elements); the later passes find their histogram in ghist.
+// The in-tile ranking is the (lane mask, count) table of the shared-memory sort (sort_rank.cu).
+constexpr int RT = 512, RE = 16, RTILE = RT * RE, RW = RT / 32;
+static_assert(LTILE % RTILE == 0, "the padded segment length must be a whole number of radix tiles");
+constexpr size_t RADIX_SMEM = (size_t)RTILE * 8 + (size_t)RW * 256 * 4 + 256 * 4 * 3 + 32 * 4;
+
+__global__ void __launch_bounds__(RT, 2) seg_radix_pass(
     const float* __restrict__ src, const uint32_t* __restrict__ kin, const uint32_t* __restrict__ iin,
-    uint32_t* __restrict__ kout, uint32_t* __restrict__ iout, const int n, const int shift, const int first)
+    uint32_t* __restrict__ kout, uint32_t* __restrict__ iout, uint32_t* __restrict__ ghist, const int n, const int pass)
 {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);      // [LTILE]
-    uint32_t* sidx = skey + LTILE;                               // [LTILE]
-    uint32_t* cnt  = sidx + LTILE;                               // [LW][256]
-    uint32_t* base = cnt + LW * 256;                             // [256] tile-local digit starts
+    uint32_t* skey = reinterpret_cast<uint32_t*>(smem_raw);      // [RTILE]
+    uint32_t* sidx = skey + RTILE;                               // [RTILE]
+    uint32_t* cnt  = sidx + RTILE;                               // [RW][256]
+    uint32_t* base = cnt + RW * 256;                             // [256] tile-local digit starts
     uint32_t* gofs = base + 256;                                 // [256] running digit offsets in the segment
     uint32_t* tot  = gofs + 256;                                 // [256]
     uint32_t* wsum = tot + 256;                                  // [32]
+    uint2*    tab  = reinterpret_cast<uint2*>(skey);             // [RW][256] ranking table, idle whenever the tile buffers are in use
 
     const int       tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t  lt  = (1u << lane) - 1u;
     const long long npd = large_pad(n);
     const long long seg = blockIdx.x;
+    const int       shift = 8 * pass;
+    const bool      first = pass == 0;
     src  += seg * n;
     kin  += seg * npd; iin += seg * npd; kout += seg * npd; iout += seg * npd;
+    ghist += seg * 768;
     uint32_t* mycnt = cnt + warp * 256;
-
-    auto key_at = [&](long long pos) -> uint32_t {
-        return first ? (pos < n ? f2key(src[pos]) : 0xffffffffu) : kin[pos];
-    };
+    uint2*    mytab = tab + warp * 256;
 
     // ---- digit histogram of the segment -> exclusive offsets
-    if (tid < 256) gofs[tid] = 0;
-    __syncthreads();
-    for (long long pos = tid; pos < npd; pos += LT) atomicAdd(&gofs[(key_at(pos) >> shift) & 255u], 1u);
+    if (first) {
+        // digits 1 and 2 into 256 counters each; the top digit (sign and exponent: a handful of values) into eight
+        // copies indexed by the lane, so that the lanes of a warp seldom add to one address
+        uint32_t* h = skey;                                      // [256] [256] [8][256]
+        if (tid < 256) gofs[tid] = 0;
+        for (int i = tid; i < 2560; i += RT) h[i] = 0;
+        __syncthreads();
+        for (long long pos = tid; pos < npd; pos += RT) {
+            const uint32_t k = pos < n ? f2key(src[pos]) : 0xffffffffu;
+            atomicAdd(&gofs[k & 255u], 1u);
+            atomicAdd(&h[(k >> 8) & 255u], 1u);
+            atomicAdd(&h[256 + ((k >> 16) & 255u)], 1u);
+            atomicAdd(&h[512 + (lane & 7) * 256 + (k >> 24)], 1u);
+        }
+        __syncthreads();
+        for (int i = tid; i < 768; i += RT) {
+            uint32_t c = h[i];
+            if (i >= 512) for (int r = 1; r < 8; r++) c += h[i + r * 256];
+            ghist[i] = c;
+        }
+    } else {
+        if (tid < 256) gofs[tid] = ghist[(pass - 1) * 256 + tid];
+    }
     __syncthreads();
     {
         uint32_t c = 0, incl = 0;
@@ -76,30 +104,25 @@ __global__ void __launch_bounds__(LT, 1) seg_radix_pass(
     }
 
     // ---- tiles in order
-    for (long long t0 = 0; t0 < npd; t0 += LTILE) {
-        uint32_t key[LE], idx[LE], rk[LE];
+    for (long long t0 = 0; t0 < npd; t0 += RTILE) {
+        uint32_t key[RE], idx[RE];
         #pragma unroll
-        for (int s = 0; s < LE; s++) {
-            const long long pos = t0 + warp * 32 * LE + s * 32 + lane;
-            key[s] = key_at(pos);
+        for (int s = 0; s < RE; s++) {
+            const long long pos = t0 + warp * 32 * RE + s * 32 + lane;
+            key[s] = first ? (pos < n ? f2key(src[pos]) : 0xffffffffu) : kin[pos];
             idx[s] = first ? (uint32_t)pos : iin[pos];
         }
-        for (int i = tid; i < LW * 256; i += LT) cnt[i] = 0;
+        for (int i = tid; i < RW * 256; i += RT) tab[i] = make_uint2(0u, 0u);
         __syncthreads();
         #pragma unroll
-        for (int s = 0; s < LE; s++) {
-            const uint32_t d     = (key[s] >> shift) & 255u;
-            uint32_t       peers = FULL;
-            #pragma unroll
-            for (int bit = 0; bit < 8; bit++) {
-                const uint32_t vote = __ballot_sync(FULL, (d >> bit) & 1u);
-                peers &= ((d >> bit) & 1u) ? vote : ~vote;
-            }
-            const int leader = __ffs(peers) - 1;
-            uint32_t  old    = 0;
-            if (lane == leader) { old = mycnt[d]; mycnt[d] = old + __popc(peers); }
-            old   = __shfl_sync(FULL, old, leader);
-            rk[s] = old + __popc(peers & lt);
+        for (int s = 0; s < RE; s++) {
+            uint2* slot = mytab + ((key[s] >> shift) & 255u);
+            atomicOr(&slot->x, 1u << lane);
+            __syncwarp();
+            const uint2 mc = *slot;
+            __syncwarp();
+            if ((mc.x & lt) == 0u) *slot = make_uint2(0u, mc.y + __popc(mc.x));
+            idx[s] |= (mc.y + __popc(mc.x & lt)) << 20;          // rank among the warp's equal digits (< 512) above the index (< 2^18)
             __syncwarp();
         }
         __syncthreads();
@@ -107,7 +130,7 @@ __global__ void __launch_bounds__(LT, 1) seg_radix_pass(
         if (tid < 256) {
             uint32_t run = 0;
             #pragma unroll 4
-            for (int w = 0; w < LW; w++) { uint32_t x = cnt[w * 256 + tid]; cnt[w * 256 + tid] = run; run += x; }
+            for (int w = 0; w < RW; w++) { const uint32_t x = tab[w * 256 + tid].y; cnt[w * 256 + tid] = run; run += x; }
             c = run; incl = run; tot[tid] = run;
             #pragma unroll
             for (int off = 1; off < 32; off <<= 1) { uint32_t t = __shfl_up_sync(FULL, incl, off); if (lane >= off) incl += t; }
@@ -117,15 +140,15 @@ __global__ void __launch_bounds__(LT, 1) seg_radix_pass(
         if (tid < 256) { uint32_t pre = 0; for (int w = 0; w < warp; w++) pre += wsum[w]; base[tid] = pre + incl - c; }
         __syncthreads();
         #pragma unroll
-        for (int s = 0; s < LE; s++) {
+        for (int s = 0; s < RE; s++) {
             const uint32_t d   = (key[s] >> shift) & 255u;
-            const uint32_t dst = base[d] + mycnt[d] + rk[s];
+            const uint32_t dst = base[d] + mycnt[d] + (idx[s] >> 20);
             skey[dst] = key[s];
-            sidx[dst] = idx[s];
+            sidx[dst] = idx[s] & 0xfffffu;
         }
         __syncthreads();
         // tile order is now digit-major: element i of digit d goes to gofs[d] + (i - base[d]), runs are contiguous
-        for (int i = tid; i < LTILE; i += LT) {
+        for (int i = tid; i < RTILE; i += RT) {
             const uint32_t k = skey[i], d = (k >> shift) & 255u;
             const uint32_t dst = gofs[d] + (uint32_t)i - base[d];
             kout[dst] = k;
@@ -340,7 +363,7 @@ size_t sort_rank_large_scratch_bytes(int nseg, int N, int M) {
     const long long np = large_pad(N);
     return (size_t)nseg * np * 4 * sizeof(uint32_t) + (size_t)nseg * N * sizeof(float)
          + (size_t)nseg * large_bstride(N) * sizeof(uint32_t) + (size_t)nseg * (N + 4) * sizeof(uint32_t)
-         + (size_t)nseg * M * sizeof(uint32_t) + 1024;
+         + (size_t)nseg * M * sizeof(uint32_t) + (size_t)nseg * 768 * sizeof(uint32_t) + 1024;
 }
 
 cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_t stream)
@@ -354,17 +377,18 @@ cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_
     uint32_t* bst  = reinterpret_cast<uint32_t*>(xs + (size_t)a.nseg * a.N);
     uint32_t* hist = bst + (size_t)a.nseg * large_bstride(a.N);
     uint32_t* rq   = hist + (size_t)a.nseg * (a.N + 4);
-    const size_t smem = (size_t)LTILE * 8 + (size_t)LW * 1024 + 256 * 4 * 3 + 32 * 4;
+    uint32_t* gh   = rq + (size_t)a.nseg * a.M;                   // digit histograms of passes 1..3, written by pass 0
+    const size_t smem = RADIX_SMEM;
     cudaError_t e = cudaFuncSetAttribute(seg_radix_pass, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     e = cudaMemsetAsync(hist, 0, sizeof(uint32_t) * (size_t)a.nseg * (a.N + 4), stream);
     if (e != cudaSuccess) return e;
 
     // the keys: four 8-bit passes, result in (k1, i1), segment stride large_pad(N)
-    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, nullptr, nullptr, k0, i0, a.N, 0, 1);
-    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k0, i0, k1, i1, a.N, 8, 0);
-    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k1, i1, k0, i0, a.N, 16, 0);
-    seg_radix_pass<<<a.nseg, LT, smem, stream>>>(a.x, k0, i0, k1, i1, a.N, 24, 0);
+    seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, nullptr, nullptr, k0, i0, gh, a.N, 0);
+    seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k0, i0, k1, i1, gh, a.N, 1);
+    seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k1, i1, k0, i0, gh, a.N, 2);
+    seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k0, i0, k1, i1, gh, a.N, 3);
     key_scalars<<<a.nseg, LT, 0, stream>>>(k1, i1, xs, bst, a);
     // the queries: ranked where they are, ordered by rank with a counting sort
     const unsigned per_query = (unsigned)((a.M + 1 + 255) / 256) * (unsigned)a.nseg;

@@ -348,10 +348,27 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum, tab);
     }
     PHASE_MARK(1);
+    // The rank search of phase (3) goes through a bucket index over the sorted keys: NB equal-width value buckets between
+    // the smallest and the largest key, bst[b] = number of keys in buckets below b. The bucket of a value is a
+    // monotone function of it, so a query's rank lies in [bst[b], bst[b + 1]] for its own bucket b and the binary
+    // search only covers that range (a handful of keys for smooth key distributions; any distribution stays
+    // correct, a degenerate one just searches a longer range). The index is filled here, while the sorted keys pass by:
+    // key j starts every bucket above its predecessor's up to its own.
+    constexpr int NB = CAP / 4;
+    const float blo = key2f(skey[0]);
+    const float bwd = key2f(skey[N - 1]) - blo;
+    const float bsc = (bwd > 1e-30f && bwd < 1e30f) ? (float)NB / bwd : 0.0f;
+    auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
     for (int j = tid; j < NP; j += THREADS) {
-        if (j < N) xs[skew(j)] = key2f(skey[j]);
+        if (j < N) {
+            const float x = key2f(skey[j]);
+            xs[skew(j)] = x;
+            const int b = bucket(x), bp = j > 0 ? bucket(key2f(skey[j - 1])) : -1;
+            for (int t = bp + 1; t <= b; t++) bst[t] = (uint16_t)j;
+        }
         xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     }
+    for (int t = bucket(key2f(skey[N - 1])) + 1 + tid; t <= NB; t += THREADS) bst[t] = (uint16_t)N;
     __syncthreads();
     PHASE_MARK(2);
     // ---- (2) per-key scalars; my run of keys is [i0, i0 + cntk). The run length is odd so that the
@@ -433,27 +450,6 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     __syncthreads();          // the su arrays are complete; skey becomes the rank histogram
     PHASE_MARK(3);
     // ---- (3) queries: rank, counting sort by rank, records
-    // The rank search goes through a bucket index over the sorted keys: NB equal-width value buckets between the
-    // smallest and the largest key, bst[b] = number of keys in buckets below b. The bucket of a value is a
-    // monotone function of it, so a query's rank lies in [bst[b], bst[b + 1]] for its own bucket b and the binary
-    // search only covers that range (a handful of keys for smooth key distributions; any distribution stays
-    // correct, a degenerate one just searches a longer range).
-    constexpr int NB = CAP / 4;
-    const float blo = xs[skew(0)];
-    const float bwd = xs[skew(N - 1)] - blo;
-    const float bsc = (bwd > 1e-30f && bwd < 1e30f) ? (float)NB / bwd : 0.0f;
-    auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
-    {
-        const int per = (N + THREADS - 1) / THREADS;
-        const int i0 = min(N, tid * per), i1 = min(N, i0 + per);
-        int prev = i0 > 0 && i0 < N ? bucket(xs[skew(i0 - 1)]) : -1;
-        for (int j = i0; j < i1; j++) {
-            const int b = bucket(xs[skew(j)]);
-            for (int t = prev + 1; t <= b; t++) bst[t] = (uint16_t)j;
-            prev = b;
-        }
-        if (i1 == N && i0 < N) for (int t = prev + 1; t <= NB; t++) bst[t] = (uint16_t)N;
-    }
     uint32_t* hist = skey;                                         // N + 1 bins
     for (int i = tid; i <= N; i += THREADS) hist[i] = 0;
     __syncthreads();

@@ -15,7 +15,6 @@ SHAPES = [(1, 1, 1, 1), (2, 3, 7, 5), (1, 2, 8, 9), (2, 2, 100, 77), (1, 3, 257,
 @pytest.mark.parametrize("shape", SHAPES)
 @pytest.mark.parametrize("mode", [0, 1])
 def test_records(shape, mode):
-    import qlka_native
     P, D, N, M = shape
     g = torch.Generator().manual_seed(N * 7 + M)
     x = torch.randn(P, D, N, generator=g) * 3
@@ -26,6 +25,64 @@ def test_records(shape, mode):
         x[0, D - 1, 3:9] = x[0, D - 1, 2]
         x[0, 0, N // 2] = -0.0
         x[0, 0, N // 2 + 1] = 0.0
+    check_records(x, y, mode)
+
+
+# Key distributions that stress the sort and the rank search rather than the arithmetic: every key equal (all lanes of a warp
+# share every digit), two values, one far outlier (the bucket index of the rank search collapses to one bucket), keys already
+# ascending / descending, values that differ only in their low mantissa bits, and infinities. Both the shared-memory kernel
+# (N = 16384, 4096) and the long-sequence kernels (N = 20000).
+KINDS = ["equal", "two_values", "outlier", "ascending", "descending", "low_bits", "infinities"]
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("N", [4096, 16384, 20000])
+def test_records_degenerate_keys(kind, N):
+    P, D, M = 1, 2, N - 37
+    g = torch.Generator().manual_seed(N + len(kind))
+    y = torch.randn(P, D, M, generator=g)
+    if kind == "equal":
+        x = torch.full((P, D, N), 0.75)
+        y[0, 0, :100] = 0.75
+    elif kind == "two_values":
+        x = torch.where(torch.rand(P, D, N, generator=g) < 0.5, torch.tensor(-1.5), torch.tensor(0.25))
+        y[0, 1, :50] = 0.25
+    elif kind == "outlier":
+        x = torch.randn(P, D, N, generator=g) * 0.01
+        x[:, :, 17] = 3.0e6
+        y = y * 0.01
+    elif kind == "ascending":
+        x = torch.linspace(-2.0, 2.0, N).repeat(P, D, 1).contiguous()
+    elif kind == "descending":
+        x = torch.linspace(2.0, -2.0, N).repeat(P, D, 1).contiguous()
+    elif kind == "low_bits":
+        x = (1.0 + torch.randint(0, 4096, (P, D, N), generator=g).float() * 2.0 ** -23)
+        y = 1.0 + torch.randint(0, 4096, (P, D, M), generator=g).float() * 2.0 ** -23
+    else:
+        x = torch.randn(P, D, N, generator=g)
+        x[:, :, 5] = float("inf")
+        x[:, :, 9] = float("-inf")
+    check_records(x, y, 1)
+    if kind not in ("infinities", "outlier"):       # (Laplace weights of infinite or 1e6-wide gaps are 0 or NaN by definition; the ranks are what is tested here)
+        check_records(x, y, 0)
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 20000, 17000), (1, 1, 40000, 300), (1, 1, 16385, 16385), (1, 1, 70001, 65536)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_records_long_segments(shape, mode):
+    P, D, N, M = shape
+    g = torch.Generator().manual_seed(N * 3 + M)
+    x = torch.randn(P, D, N, generator=g) * 2
+    y = torch.randn(P, D, M, generator=g) * 2
+    x[0, 0, 3:9] = x[0, 0, 2]
+    x[0, 0, :4] = y[0, 0, :4]
+    check_records(x, y, mode)
+
+
+def check_records(x, y, mode):
+    import qlka_native
+    P, D, N = x.shape
+    M = y.shape[2]
     xperm, xval, yrec, mstart = (t.cpu().numpy() for t in qlka_native.sort_rank_records(x.cuda(), y.cuda(), mode))
     torch.cuda.synchronize()
     NBK = N // 8 + 1

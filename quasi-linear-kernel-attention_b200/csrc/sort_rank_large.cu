@@ -23,10 +23,8 @@
 
 namespace qlka {
 
-constexpr int LT = 1024;            // threads
 constexpr int LE = 16;              // elements per thread and tile
-constexpr int LTILE = LT * LE;      // 16384
-constexpr int LW = LT / 32;
+constexpr int LTILE = 1024 * LE;    // 16384: the segments' (key, index) buffers are padded to a multiple of this
 
 __host__ __device__ inline long long large_pad(int n) { return ((long long)n + LTILE - 1) / LTILE * LTILE; }
 
@@ -161,7 +159,7 @@ __global__ void __launch_bounds__(RT, 2) seg_radix_pass(
 }
 
 // Sorted keys of every segment -> xs (float, [seg][N]), xperm, xval and the scalar scans su0 / su1.
-// One CTA per segment, tiles of LT * LE keys, each thread a contiguous run of LE keys within the tile.
+// One CTA per segment, tiles of ST * LE keys.
 // Bucket index of the rank search: LNB(N) equal-width value buckets between the smallest and the largest key of a
 // segment; bst[b] = number of keys in buckets below b, bst[LNB] = N. The bucket of a value is monotone in the value,
 // so the rank of a query lies in [bst[b], bst[b + 1]] for its own bucket b.
@@ -178,7 +176,11 @@ struct BucketMap {
     __device__ __forceinline__ int operator()(const float v) const { return (int)fminf(fmaxf((v - lo) * scale, 0.0f), (float)(nb - 1)); }
 };
 
-__global__ void __launch_bounds__(LT, 1) key_scalars(
+// The per-segment scan kernels (key_scalars, scan_starts) walk their segment tile by tile with a carried state, so a CTA has
+// little in flight at any moment: 512 threads and two CTAs per SM, and the loads of a batch of iterations issued before its stores.
+constexpr int ST = 512, STILE = ST * LE;
+
+__global__ void __launch_bounds__(ST, 2) key_scalars(
     const uint32_t* __restrict__ ksorted, const uint32_t* __restrict__ isorted, float* __restrict__ xs_all,
     uint32_t* __restrict__ bst_all, const SortArgs a)
 {
@@ -200,18 +202,31 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
     {
         const BucketMap bucket(key2f(ksorted[0]), key2f(ksorted[N - 1]), N);
         uint32_t* bst = bst_all + seg * large_bstride(N);
-        for (int j = tid; j < NP + KB; j += LT) {
-            if (j < N) {
-                const float x = key2f(ksorted[j]), xp = j > 0 ? key2f(ksorted[j - 1]) : 0.0f;
-                xs[j] = x;
-                const int b = bucket(x), prev = j > 0 ? bucket(xp) : -1;
-                for (int t = prev + 1; t <= b; t++) bst[t] = (uint32_t)j;
-                if (j == N - 1) for (int t = b + 1; t <= bucket.nb; t++) bst[t] = (uint32_t)N;
-                if (a.mode != MODE_SGN) xval[j] = lap ? (j > 0 ? decay_of(x - xp) : 0.0f) : x;
-            } else if (a.mode != MODE_SGN) {
-                xval[j] = lap ? 1.0f : 0.0f;
+        constexpr int U = 4;
+        for (int j0 = tid; j0 < NP + KB; j0 += ST * U) {
+            uint32_t kj[U], kp[U], ij[U];
+            #pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int j = j0 + u * ST;
+                kj[u] = j < N ? ksorted[j] : 0u;
+                kp[u] = (j > 0 && j < N) ? ksorted[j - 1] : 0u;
+                ij[u] = j < N ? isorted[j] : 0u;
             }
-            if (j < NP) xperm[j] = j < N ? isorted[j] : 0u;
+            #pragma unroll
+            for (int u = 0; u < U; u++) {
+                const int j = j0 + u * ST;
+                if (j < N) {
+                    const float x = key2f(kj[u]), xp = j > 0 ? key2f(kp[u]) : 0.0f;
+                    xs[j] = x;
+                    const int b = bucket(x), prev = j > 0 ? bucket(xp) : -1;
+                    for (int t = prev + 1; t <= b; t++) bst[t] = (uint32_t)j;
+                    if (j == N - 1) for (int t = b + 1; t <= bucket.nb; t++) bst[t] = (uint32_t)N;
+                    if (a.mode != MODE_SGN) xval[j] = lap ? (j > 0 ? decay_of(x - xp) : 0.0f) : x;
+                } else if (j < NP + KB && a.mode != MODE_SGN) {
+                    xval[j] = lap ? 1.0f : 0.0f;
+                }
+                if (j < NP) xperm[j] = ij[u];
+            }
         }
     }
     if (a.scal != SCAL_UNIT && a.scal != SCAL_PREFIX && a.scal != SCAL_SIGNED) return;
@@ -228,7 +243,7 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
         if (tid == 0) carry[0] = 0.0f;
         __syncthreads();
         float* dst = dir ? su1 : su0;
-        for (long long t0 = 0; t0 < N; t0 += LTILE) {
+        for (long long t0 = 0; t0 < N; t0 += STILE) {
             // scan position i (0-based in scan order) <-> key j = i (forward) or N-1-i (backward)
             float ta[LE], tb[LE];                     // state at position (k, lane) = ta * (state entering the warp's chunk) + tb
             float ca = 1.0f, cb = 0.0f;               // the same for the end of the previous row
@@ -262,7 +277,7 @@ __global__ void __launch_bounds__(LT, 1) key_scalars(
                 if (i < N) dst[dir ? N - 1 - (int)i : (int)i] = fmaf(ta[k], x0, tb[k]);
             }
             __syncthreads();
-            if (tid == LT - 32) carry[0] = fmaf(ca, x0, cb);      // (lane 0 of the last warp) state after the tile; padding positions are identity
+            if (tid == ST - 32) carry[0] = fmaf(ca, x0, cb);      // (lane 0 of the last warp) state after the tile; padding positions are identity
             __syncthreads();
         }
     }
@@ -290,7 +305,7 @@ __global__ void __launch_bounds__(256) rank_queries(
 }
 
 // ---- exclusive scan of the rank histogram (N + 1 bins) in place; mstart[b] = start of rank b * KB
-__global__ void __launch_bounds__(LT, 1) scan_starts(uint32_t* __restrict__ hist_all, const SortArgs a)
+__global__ void __launch_bounds__(ST, 2) scan_starts(uint32_t* __restrict__ hist_all, const SortArgs a)
 {
     __shared__ uint32_t wsum[32], carry;
     const int       tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -300,7 +315,7 @@ __global__ void __launch_bounds__(LT, 1) scan_starts(uint32_t* __restrict__ hist
     uint32_t* ms   = a.mstart + seg * mstride(N);
     if (tid == 0) { carry = 0; ms[NBK] = (uint32_t)a.M; }
     __syncthreads();
-    for (int t0 = 0; t0 <= N; t0 += LT * KB) {
+    for (int t0 = 0; t0 <= N; t0 += ST * KB) {
         const int i0 = t0 + tid * KB;                           // a thread's run starts on a block boundary
         uint32_t c[KB], run = 0;
         #pragma unroll
@@ -316,7 +331,7 @@ __global__ void __launch_bounds__(LT, 1) scan_starts(uint32_t* __restrict__ hist
         #pragma unroll
         for (int k = 0; k < KB; k++) { if (i0 + k <= N) hist[i0 + k] = pre; pre += c[k]; }
         __syncthreads();
-        if (tid == LT - 1) carry = pre;
+        if (tid == ST - 1) carry = pre;
         __syncthreads();
     }
 }
@@ -389,11 +404,11 @@ cudaError_t launch_sort_rank_large(const SortArgs& a, void* scratch, cudaStream_
     seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k0, i0, k1, i1, gh, a.N, 1);
     seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k1, i1, k0, i0, gh, a.N, 2);
     seg_radix_pass<<<a.nseg, RT, smem, stream>>>(a.x, k0, i0, k1, i1, gh, a.N, 3);
-    key_scalars<<<a.nseg, LT, 0, stream>>>(k1, i1, xs, bst, a);
+    key_scalars<<<a.nseg, ST, 0, stream>>>(k1, i1, xs, bst, a);
     // the queries: ranked where they are, ordered by rank with a counting sort
     const unsigned per_query = (unsigned)((a.M + 1 + 255) / 256) * (unsigned)a.nseg;
     rank_queries<<<per_query, 256, 0, stream>>>(xs, bst, rq, hist, a);
-    scan_starts<<<a.nseg, LT, 0, stream>>>(hist, a);
+    scan_starts<<<a.nseg, ST, 0, stream>>>(hist, a);
     place_records<<<per_query, 256, 0, stream>>>(xs, rq, hist, a);
     return cudaGetLastError();
 }

@@ -65,16 +65,16 @@ int qlka_weighted_laplace_sum_forward(const float* q, const float* k, const floa
                                       int P, int D, int N, int M, int C, qlka_stream_t stream);
 
 /* The same operator for callers that cannot hand over a workspace and must not trigger an
- * allocation: code running between cudaStreamBeginCapture and EndCapture, latency-critical
- * serving loops (cudaMalloc serialises the whole device), and hosts whose own memory pool already
- * owns all of HBM. The scratch is a fixed array of qlka_noalloc_scratch_bytes() (32 MiB) inside
+ * allocation: latency-critical serving loops (cudaMalloc serialises the whole device) and hosts
+ * whose own memory pool already owns all of HBM. (Nothing is claimed about recording the call into
+ * a CUDA graph: that has not been tested.) The scratch is a fixed array of qlka_noalloc_scratch_bytes() (32 MiB) inside
  * the library image; every GPU that loads the library keeps that much reserved until the process
  * exits. Problems whose scratch would not fit are refused with QLKA_ERR_NO_ALLOC_LIMIT (roughly:
  * P*D*(N+M) above a few hundred thousand elements) - use the workspace variant for those. The call
  * allocates nothing and frees nothing once the array exists: with CUDA's default lazy module loading
  * the array is materialised by the first call on each device (which looks up its device address), or
  * at load time under CUDA_MODULE_LOADING=EAGER. So make one call per device at start-up, before the
- * host's own pool has taken the memory and outside any stream capture; that first call is the one that
+ * host's own pool has taken the memory; that first call is the one that
  * can fail with QLKA_ERR_CUDA (out of memory), later ones leave free device memory untouched. All calls
  * share the one array: two calls whose kernels can overlap on the GPU (different streams, or
  * different host threads) corrupt each other, so serialise them. Nothing needs to be cleared

@@ -1,5 +1,5 @@
-"""The entry point that brings its own scratch (for callers that may not allocate: stream
-capture, serving loops, hosts that own all device memory). Collected last on purpose.
+"""The entry point that brings its own scratch (for callers that may not allocate:
+serving loops, hosts that own all device memory). Collected last on purpose.
 
 Called through the C ABI, twice in a row with different problems, and compared with the
 workspace entry point on the same inputs. The second call runs on scratch that still holds the

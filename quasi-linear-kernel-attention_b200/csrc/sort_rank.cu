@@ -1,7 +1,8 @@
 // Sort/rank kernel for segments of up to 16384 keys and queries: one CTA per segment sorts
-// the keys and then the queries with a stable LSD radix sort that lives entirely in shared
-// memory (8-bit digits, keys carried with their 16-bit index), ranks every query among the
-// keys, and writes the walk records described in qlka_common.cuh.
+// the keys with a stable LSD radix sort that lives entirely in shared memory (8-bit digits,
+// keys carried with their 16-bit index), ranks every query among the keys (the queries are
+// not sorted by value: a bucket index over the sorted keys, a short binary search, then a
+// counting sort by rank), and writes the walk records described in qlka_common.cuh.
 //
 // The reference does this step with two CUB segmented radix sorts through global memory
 // (Weighted_Laplace_Sum/csrc/sort_utils.cu:23-81, Weighted_Abs_Sum/csrc/sort_utils.cu:18-75,

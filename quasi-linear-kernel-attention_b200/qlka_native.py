@@ -185,6 +185,16 @@ class HostPipeline:
                          for _ in range(2)]
             self.s_in, self.s_run, self.s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
 
+    def _ranges(self, P):
+        """Head ranges of the chunks: full chunks, then halves of what is left, so that the work that nothing overlaps
+        (the kernels and the read-back of the last chunk) is that of a single head."""
+        lo = 0
+        while lo < P:
+            left = P - lo
+            n = self.chunk if left > self.chunk else max(1, left // 2)
+            yield lo, lo + n
+            lo += n
+
     def __call__(self, q_h, k_h, v_h, out_w_h, out_u_h):
         """Enqueue one pass over all heads; returns after everything has been enqueued. The caller
         synchronises (e.g. torch.cuda.synchronize()) before reading out_w_h / out_u_h."""
@@ -194,8 +204,8 @@ class HostPipeline:
         for s in (self.s_in, self.s_run, self.s_out):
             s.wait_stream(cur)
         with torch.cuda.device(self.device):
-            for i, lo in enumerate(range(0, P, self.chunk)):
-                hi, b = min(P, lo + self.chunk), self.sets[i % 2]
+            for i, (lo, hi) in enumerate(self._ranges(P)):
+                b = self.sets[i % 2]
                 n = hi - lo
                 with torch.cuda.stream(self.s_in):
                     self.s_in.wait_event(b["computed"])          # the previous user of this buffer set has consumed its inputs

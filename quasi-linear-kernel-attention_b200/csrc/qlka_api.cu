@@ -4,6 +4,7 @@
 #include "../../include/qlka.h"
 #include "qlka_common.cuh"
 
+#include <atomic>
 #include <climits>
 
 namespace qlka {
@@ -72,19 +73,18 @@ struct Bump {
     }
 };
 
-// SM count of the current device, looked up once per device (racing first calls store the same value; int stores
-// are atomic on every host this library builds for)
+// SM count of the current device, looked up once per device (racing first calls store the same value)
 int sm_count() {
     constexpr int MAX_DEV = 64;
-    static int cached[MAX_DEV] = {};
+    static std::atomic<int> cached[MAX_DEV];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 148;      // B200; keeps workspace sizes defined without a device
-    if (!cached[dev]) {
-        int n = 0;
+    int n = cached[dev].load(std::memory_order_acquire);
+    if (!n) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        cached[dev].store(n, std::memory_order_release);
     }
-    return cached[dev];
+    return n;
 }
 
 // How a walk over `nseg` segments of N keys is cut into streams, work items and CTAs. Streams are independent
@@ -656,16 +656,16 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[QLKA_NOALLOC_SC
 // use: the device address is looked up once per device (with that device current) and cached.
 static int noalloc_scratch(void** out) {
     constexpr int MAX_DEV = 64;
-    static void* cached[MAX_DEV] = {};
+    static std::atomic<void*> cached[MAX_DEV];
     int dev = 0;
     CU(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MAX_DEV) return QLKA_ERR_UNSUPPORTED;
-    if (!cached[dev]) {
-        void* ptr = nullptr;
+    void* ptr = cached[dev].load(std::memory_order_acquire);
+    if (!ptr) {
         CU(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
-        cached[dev] = ptr;      // racing first calls store the same value (pointer stores are atomic on the hosts this builds for)
+        cached[dev].store(ptr, std::memory_order_release);      // racing first calls store the same value
     }
-    *out = cached[dev];
+    *out = ptr;
     return QLKA_OK;
 }
 

@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     uint32_t* cnt  = reinterpret_cast<uint32_t*>(wb + 32);          // per-warp digit counters ...
     uint16_t* sidx = reinterpret_cast<uint16_t*>(cnt + W * 256);    // ... and the index payload; together >= 4 * CAP bytes
     float*    su0s = reinterpret_cast<float*>(cnt);                 // Laplace: forward unit scan, once both are idle
-    uint16_t* bst  = sidx + CAP;                                    // bucket index of the rank search, CAP / 4 + 2 entries
+    uint16_t* bst  = sidx + CAP;                                    // bucket counters, then bucket starts: CAP / 2 + 1 entries (+ padding)
     uint2*    tab  = reinterpret_cast<uint2*>(xs);                  // (mask, count) table of the radix sort (E = 16), idle by the time xs is filled
 
     const int tid = threadIdx.x;
@@ -342,34 +342,131 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     float*    su1    = a.su1 ? a.su1 + (long long)seg * (N + 1) : nullptr;
     PHASE_BEGIN();
     // ---- (1) keys
+    // NB equal-width value buckets between the smallest and the largest key; the bucket of a value is a monotone
+    // function of it. They serve twice. Sorting: when no bucket holds more than RUN_LIMIT keys (any smooth
+    // distribution), the keys are counted into their buckets, scattered to the buckets' ranges and ranked inside
+    // their bucket by counting the smaller ones - one pass and a short loop per key instead of four radix passes;
+    // otherwise (clustered keys, an outlier that stretches the range, infinities) the radix sort runs.
+    // Rank search of phase (3): bst[b] = number of keys in buckets below b, so a query's rank lies in
+    // [bst[b], bst[b + 1]] for its own bucket b and the binary search only covers that range.
+    constexpr int      NB        = CAP / 2;
+    constexpr uint32_t RUN_LIMIT = 64;
+    float blo, bsc;
+    auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
+    bool by_radix;
     {
         uint32_t key[E], idx[E];
         load_segment<THREADS, E>(a.x + (long long)seg * N, N, key, idx);
         PHASE_MARK(0);
-        block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum, tab);
+        const int warp = tid >> 5, lane = tid & 31;
+        uint32_t* hw = reinterpret_cast<uint32_t*>(bst);           // the bucket counters: NB + 1 of 16 bits, two to a word
+        {
+            uint32_t kmin = 0xffffffffu, kmax = 0u;                // (the key order is the value order)
+            #pragma unroll
+            for (int s = 0; s < E; s++)
+                if (warp * 32 * E + s * 32 + lane < N) { kmin = min(kmin, key[s]); kmax = max(kmax, key[s]); }
+            #pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(FULL, kmin, off));
+                kmax = max(kmax, __shfl_xor_sync(FULL, kmax, off));
+            }
+            if (lane == 0) { base[warp] = kmin; base[32 + warp] = kmax; }
+            for (int i = tid; i < NB / 2 + 1; i += THREADS) hw[i] = 0u;
+            __syncthreads();
+            kmin = lane < W ? base[lane] : 0xffffffffu;
+            kmax = lane < W ? base[32 + lane] : 0u;
+            #pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(FULL, kmin, off));
+                kmax = max(kmax, __shfl_xor_sync(FULL, kmax, off));
+            }
+            blo = key2f(kmin);
+            const float bwd = key2f(kmax) - blo;
+            bsc = (bwd > 1e-30f && bwd < 1e30f) ? (float)NB / bwd : 0.0f;
+        }
+        // count: the returned old value is the key's place among its bucket's keys (in arrival order)
+        #pragma unroll
+        for (int s = 0; s < E; s++) {
+            if (warp * 32 * E + s * 32 + lane < N) {
+                const uint32_t bk  = (uint32_t)bucket(key2f(key[s])), sh = (bk & 1u) * 16u;
+                const uint32_t old = atomicAdd(&hw[bk >> 1], 1u << sh);            // (a bucket holds at most N <= 16384 keys: no carry)
+                idx[s] = bk | (((old >> sh) & 0xffffu) << 16);
+            }
+        }
+        __syncthreads();
+        // bucket starts: exclusive scan of the NB + 1 counters in place (the last one counts nothing, so bst[NB] = N)
+        {
+            constexpr int PER = (NB + 1 + THREADS - 1) / THREADS;
+            const int i0 = min(NB + 1, tid * PER), i1 = min(NB + 1, i0 + PER);
+            uint32_t run = 0, big = 0;
+            for (int i = i0; i < i1; i++) { const uint32_t c = bst[i]; run += c; big |= c > RUN_LIMIT; }
+            uint32_t incl = run;
+            #pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const uint32_t t = __shfl_up_sync(FULL, incl, off);
+                if (lane >= off) incl += t;
+            }
+            if (lane == 31) wsum[warp] = incl;
+            by_radix = __syncthreads_or((int)big) != 0;
+            uint32_t pre = incl - run;
+            for (int w = 0; w < warp; w++) pre += wsum[w];
+            for (int i = i0; i < i1; i++) { const uint32_t c = bst[i]; bst[i] = (uint16_t)pre; pre += c; }
+        }
+        __syncthreads();
+        if (!by_radix) {
+            #pragma unroll
+            for (int s = 0; s < E; s++) {
+                const int pos = warp * 32 * E + s * 32 + lane;
+                if (pos < N) {
+                    const uint32_t dst = (uint32_t)bst[idx[s] & 0xffffu] + (idx[s] >> 16);
+                    skey[dst] = key[s];
+                    sidx[dst] = (uint16_t)pos;
+                }
+            }
+            __syncthreads();
+            // final place of the key at p: start of its bucket + the keys of the bucket that sort before it (equal keys in
+            // the order of their original index, as the radix sort leaves them)
+            uint16_t* sidx2 = reinterpret_cast<uint16_t*>(cnt);
+            #pragma unroll 2
+            for (int s = 0; s < E; s++) {
+                const int pp = warp * 32 * E + s * 32 + lane;
+                if (pp < N) {
+                    const uint32_t k   = skey[pp], mine = sidx[pp];
+                    const float    x   = key2f(k);
+                    const int      bk  = bucket(x);
+                    const int      lo  = bst[bk], hi = bst[bk + 1];
+                    int            c   = 0;
+                    for (int j = lo; j < hi; j++) {
+                        const uint32_t kk = skey[j];
+                        c += kk < k;
+                        if (kk == k && j != pp) c += sidx[j] < mine;
+                    }
+                    xs[skew(lo + c)] = x;
+                    sidx2[lo + c]    = (uint16_t)mine;
+                }
+            }
+            __syncthreads();
+            for (int j = tid; j < N; j += THREADS) sidx[j] = sidx2[j];
+        } else {
+            #pragma unroll
+            for (int s = 0; s < E; s++) idx[s] = warp * 32 * E + s * 32 + lane;
+            block_radix_sort<THREADS, E>(key, idx, skey, sidx, cnt, base, wsum, tab);
+        }
     }
     PHASE_MARK(1);
-    // The rank search of phase (3) goes through a bucket index over the sorted keys: NB equal-width value buckets between
-    // the smallest and the largest key, bst[b] = number of keys in buckets below b. The bucket of a value is a
-    // monotone function of it, so a query's rank lies in [bst[b], bst[b + 1]] for its own bucket b and the binary
-    // search only covers that range (a handful of keys for smooth key distributions; any distribution stays
-    // correct, a degenerate one just searches a longer range). The index is filled here, while the sorted keys pass by:
-    // key j starts every bucket above its predecessor's up to its own.
-    constexpr int NB = CAP / 4;
-    const float blo = key2f(skey[0]);
-    const float bwd = key2f(skey[N - 1]) - blo;
-    const float bsc = (bwd > 1e-30f && bwd < 1e30f) ? (float)NB / bwd : 0.0f;
-    auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
-    for (int j = tid; j < NP; j += THREADS) {
-        if (j < N) {
+    if (by_radix) {
+        // sorted keys to floats; the bucket starts again, now from the sorted order: key j starts every bucket above its
+        // predecessor's up to its own
+        for (int j = tid; j < N; j += THREADS) {
             const float x = key2f(skey[j]);
             xs[skew(j)] = x;
             const int b = bucket(x), bp = j > 0 ? bucket(key2f(skey[j - 1])) : -1;
             for (int t = bp + 1; t <= b; t++) bst[t] = (uint16_t)j;
         }
-        xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
+        for (int t = bucket(key2f(skey[N - 1])) + 1 + tid; t <= NB; t += THREADS) bst[t] = (uint16_t)N;
     }
-    for (int t = bucket(key2f(skey[N - 1])) + 1 + tid; t <= NB; t += THREADS) bst[t] = (uint16_t)N;
+    __syncthreads();
+    for (int j = tid; j < NP; j += THREADS) xperm[j] = j < N ? (uint32_t)sidx[j] : 0u;
     __syncthreads();
     PHASE_MARK(2);
     // ---- (2) per-key scalars; my run of keys is [i0, i0 + cntk). The run length is odd so that the
@@ -593,7 +690,7 @@ static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2
-                      + (size_t)(CAP / 4 + 8) * 2;
+                      + (size_t)(CAP / 2 + 8) * 2;
     auto kern = sort_rank_small<THREADS, E, VAR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -309,6 +309,13 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 //   VAR_ABS_FOLD    abs records over folded (shifted, weighted) query copies
 enum SortVariant : int { VAR_LAP = 0, VAR_LAP_SIGNED = 1, VAR_ABS = 2, VAR_ABS_FOLD = 3 };
 
+// Value buckets per segment (see phase (1) of the kernel): the more, the shorter the in-bucket ranking and the rank search.
+// The 1024-thread kernel has its SM to itself and takes what its shared memory still holds (just under one bucket per
+// element); the smaller ones stay at half their capacity, which keeps four CTAs on an SM.
+__host__ __device__ constexpr int sort_buckets(int threads, int e) {
+    return threads == 1024 ? threads * e - threads * e / 32 : threads * e / 2;
+}
+
 template <int THREADS, int E, int VAR>
 __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const SortArgs a)
 {
@@ -325,7 +332,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     uint32_t* cnt  = reinterpret_cast<uint32_t*>(wb + 32);          // per-warp digit counters ...
     uint16_t* sidx = reinterpret_cast<uint16_t*>(cnt + W * 256);    // ... and the index payload; together >= 4 * CAP bytes
     float*    su0s = reinterpret_cast<float*>(cnt);                 // Laplace: forward unit scan, once both are idle
-    uint16_t* bst  = sidx + CAP;                                    // bucket counters, then bucket starts: CAP / 2 + 1 entries (+ padding)
+    uint16_t* bst  = sidx + CAP;                                    // bucket counters, then bucket starts: sort_buckets() + 1 entries (+ padding)
     uint2*    tab  = reinterpret_cast<uint2*>(xs);                  // (mask, count) table of the radix sort (E = 16), idle by the time xs is filled
 
     const int tid = threadIdx.x;
@@ -349,7 +356,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
     // otherwise (clustered keys, an outlier that stretches the range, infinities) the radix sort runs.
     // Rank search of phase (3): bst[b] = number of keys in buckets below b, so a query's rank lies in
     // [bst[b], bst[b + 1]] for its own bucket b and the binary search only covers that range.
-    constexpr int      NB        = CAP / 2;
+    constexpr int      NB        = sort_buckets(THREADS, E);
     constexpr uint32_t RUN_LIMIT = 64;
     float blo, bsc;
     auto bucket = [&](const float val) -> int { return (int)fminf(fmaxf((val - blo) * bsc, 0.0f), (float)(NB - 1)); };
@@ -396,7 +403,7 @@ __global__ void __launch_bounds__(THREADS, 1024 / THREADS) sort_rank_small(const
         __syncthreads();
         // bucket starts: exclusive scan of the NB + 1 counters in place (the last one counts nothing, so bst[NB] = N)
         {
-            constexpr int PER = (NB + 1 + THREADS - 1) / THREADS;
+            constexpr int PER = ((NB + 1 + THREADS - 1) / THREADS) | 1;      // odd: a thread's run of 16-bit counters starts in a bank of its own
             const int i0 = min(NB + 1, tid * PER), i1 = min(NB + 1, i0 + PER);
             uint32_t run = 0, big = 0;
             for (int i = i0; i < i1; i++) { const uint32_t c = bst[i]; run += c; big |= c > RUN_LIMIT; }
@@ -690,7 +697,7 @@ static cudaError_t launch_inst(const SortArgs& a, cudaStream_t stream) {
     constexpr int CAP = THREADS * E;
     constexpr int W   = THREADS / 32;
     const size_t smem = (size_t)CAP * 4 * 2 + 32 * 4 + (size_t)(CAP / 32 + 32) * 4 + (size_t)W * 256 * 4 + 256 * 4 + 32 * 4 * 3 + (size_t)CAP * 2
-                      + (size_t)(CAP / 2 + 8) * 2;
+                      + (size_t)(sort_buckets(THREADS, E) + 8) * 2;
     auto kern = sort_rank_small<THREADS, E, VAR>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

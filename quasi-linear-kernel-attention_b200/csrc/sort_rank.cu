@@ -1,8 +1,9 @@
 // Sort/rank kernel for segments of up to 16384 keys and queries: one CTA per segment sorts
-// the keys with a stable LSD radix sort that lives entirely in shared memory (8-bit digits,
-// keys carried with their 16-bit index), ranks every query among the keys (the queries are
-// not sorted by value: a bucket index over the sorted keys, a short binary search, then a
-// counting sort by rank), and writes the walk records described in qlka_common.cuh.
+// the keys in shared memory (by equal-width value buckets and a ranking inside each bucket,
+// or, when the keys crowd into few buckets, with a stable LSD radix sort on 8-bit digits; keys
+// carried with their 16-bit index), ranks every query among the keys (the queries are not
+// sorted by value: the bucket starts as an index, a short binary search, then a counting sort
+// by rank), and writes the walk records described in qlka_common.cuh.
 //
 // The reference does this step with two CUB segmented radix sorts through global memory
 // (Weighted_Laplace_Sum/csrc/sort_utils.cu:23-81, Weighted_Abs_Sum/csrc/sort_utils.cu:18-75,
@@ -294,7 +295,7 @@ __device__ __forceinline__ int lower_bound_f(const float* __restrict__ a, const 
 }
 
 // ------------------------------------------------------------------ the kernel
-// Phases: (1) radix sort of the keys; (2) per-key decays and the scalar scans, each thread on a
+// Phases: (1) sort of the keys (value buckets, or the radix sort above); (2) per-key decays and the scalar scans, each thread on a
 // contiguous run of keys with the decays in registers; (3) the queries are not sorted by value:
 // each is ranked against the sorted keys by binary search and the records are ordered by rank
 // with a counting sort (shared-memory histogram over the N + 1 ranks, exclusive scan, atomic

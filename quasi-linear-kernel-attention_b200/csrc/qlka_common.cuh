@@ -92,6 +92,15 @@ __device__ __forceinline__ float key2f(uint32_t u) {
 // thousand ulps of 1 and thousands of them multiply into every prefix state, so their rounding error is
 // what limits the accuracy of the Laplace recurrences; expf alone is off by up to 2 ulp there
 __device__ __forceinline__ float decay_of(const float gap) {
+    if (gap < 0.0625f) {
+        // the usual case with thousands of keys: 1 - g + g^2/2 - ... - g^5/120 (the next term is below 1e-10 here); the
+        // polynomial's own rounding is scaled by g, so the result is the exact value rounded once, to within 0.6 ulp
+        float p = fmaf(gap, -1.0f / 120.0f, 1.0f / 24.0f);
+        p = fmaf(gap, p, -1.0f / 6.0f);
+        p = fmaf(gap, p, 0.5f);
+        p = fmaf(gap, p, -1.0f);
+        return fmaf(gap, p, 1.0f);
+    }
     return gap < 0.5f ? 1.0f + expm1f(-gap) : expf(-gap);
 }
 

@@ -28,11 +28,11 @@ def test_records(shape, mode):
     check_records(x, y, mode)
 
 
-# Key distributions that stress the sort and the rank search rather than the arithmetic: every key equal (all lanes of a warp
-# share every digit), two values, one far outlier (the bucket index of the rank search collapses to one bucket), keys already
+# Key distributions that stress the sort and the rank search rather than the arithmetic: every key equal (one value bucket holds
+# everything, and in the radix sort all lanes of a warp share every digit), two values, one far outlier (the bucket index of the rank search collapses to one bucket), keys already
 # ascending / descending, values that differ only in their low mantissa bits, and infinities. Both the shared-memory kernel
 # (N = 16384, 4096) and the long-sequence kernels (N = 20000).
-KINDS = ["equal", "two_values", "outlier", "ascending", "descending", "low_bits", "infinities"]
+KINDS = ["equal", "two_values", "outlier", "ascending", "descending", "low_bits", "infinities", "clump_40", "clump_200"]
 
 
 @pytest.mark.parametrize("kind", KINDS)
@@ -58,6 +58,13 @@ def test_records_degenerate_keys(kind, N):
     elif kind == "low_bits":
         x = (1.0 + torch.randint(0, 4096, (P, D, N), generator=g).float() * 2.0 ** -23)
         y = 1.0 + torch.randint(0, 4096, (P, D, M), generator=g).float() * 2.0 ** -23
+    elif kind.startswith("clump"):
+        # a group of equal keys inside smooth ones: 40 stay under the bucket sort's limit of 64 keys per bucket (ties are then
+        # ranked inside the bucket), 200 send the segment to the radix sort
+        x = torch.randn(P, D, N, generator=g)
+        n = int(kind.split("_")[1])
+        x[:, :, 100:100 + n] = 0.123
+        y[0, 0, :30] = 0.123
     else:
         x = torch.randn(P, D, N, generator=g)
         x[:, :, 5] = float("inf")
